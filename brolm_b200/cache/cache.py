@@ -17,7 +17,12 @@ Layers whose needs are equal form a *group* with storage of its own:
   of that row size;
 * a group that sees a chunk of C keys (position p sees the keys from
   ``p - p % C`` on) holds the same ring as a window of C: a chunk never spans
-  more places than the ring has.
+  more places than the ring has;
+* a windowed group that also keeps a sequence's first F keys visible for good
+  (``keep_first``) holds ``round_up(F, page_size)`` places ahead of the ring:
+  position p lives at place p below that bound and at
+  ``head + (p - head) % ring`` from it on (``KVGroup.place``), so the first
+  pages of a sequence are never written again.
 
 A schedule entry may keep several things at once (a mixer made of two: keys
 and values for one, a state for the other): its spec is then a tuple of specs
@@ -55,6 +60,7 @@ class KVSpec:
     values: bool = True
     v_dim: Optional[int] = None      # size of a value row when it is not head_dim
     chunk: Optional[int] = None      # position p sees keys p - p % chunk .. p: kept like a window of that many
+    keep_first: int = 0              # with a window: the first keys of a sequence that stay visible however far back
 
 
 @dataclasses.dataclass(frozen=True)
@@ -83,6 +89,8 @@ class KVGroup:
         self.entries = entries
         self.page_size = page_size
         self.ring = _round_up(kept_span(spec), page_size) if kept_span(spec) else None
+        # places ahead of the ring that are held for good (the first keys a window keeps)
+        self.head = _round_up(spec.keep_first, page_size) if (self.ring and spec.keep_first) else 0
         self.pool = PagePool(num_pages)
         shape = (len(entries), num_pages, spec.n_kv, page_size, spec.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
@@ -98,8 +106,19 @@ class KVGroup:
         return self.ring if self.ring else (1 << 30)
 
     def pages_for(self, length: int) -> int:
-        held = length if self.ring is None else min(length, self.ring)
+        held = length if self.ring is None else min(length, self.head + self.ring)
         return (held + self.page_size - 1) // self.page_size
+
+    def place(self, pos):
+        """Where position ``pos`` (a number or an array) lives among a sequence's places."""
+        if self.ring is None:
+            return pos
+        if not self.head:
+            return pos % self.ring
+        import numpy as np
+        if isinstance(pos, np.ndarray):
+            return np.where(pos < self.head, pos, self.head + (pos - self.head) % self.ring)
+        return pos if pos < self.head else self.head + (pos - self.head) % self.ring
 
 
 class StateGroup:
@@ -185,7 +204,7 @@ class Cache:
             if isinstance(spec, KVSpec):
                 pages = self.num_pages
                 if kept_span(spec):
-                    ring_pages = _round_up(kept_span(spec), page_size) // page_size
+                    ring_pages = (_round_up(kept_span(spec), page_size) + _round_up(spec.keep_first, page_size)) // page_size
                     pages = min(pages, self.max_slots * ring_pages)
                 g = KVGroup(spec, [i for i, _ in idxs], pages, page_size, dtype, self.device)
                 gid = len(self.kv_groups)
@@ -286,11 +305,11 @@ class Cache:
                 out.append(np.full(b - a, -1, dtype=np.int64))
                 continue
             pos = np.arange(a, b, dtype=np.int64)
-            ridx = pos % g.ring if g.ring else pos
+            ridx = g.place(pos)
             pages = np.asarray(g.pages[s], dtype=np.int64)
             rows = pages[ridx // g.page_size] * g.page_size + ridx % g.page_size
             if g.ring:
-                rows[pos < b - g.ring] = -1
+                rows[(pos < b - g.ring) & (pos >= g.head)] = -1
             out.append(rows)
         return np.concatenate(out) if out else np.zeros(0, dtype=np.int64)
 
@@ -303,13 +322,13 @@ class Cache:
     def decode_rows(self, group_id: int, slots: Sequence[int], positions: Sequence[int]) -> list:
         """``write_rows`` for one new token per slot at ``positions`` (the decode step), without arrays."""
         g = self.kv_groups[group_id]
-        P, ring = g.page_size, g.ring
+        P = g.page_size
         out = []
         for s, pos in zip(slots, positions):
             if s < 0:
                 out.append(-1)
                 continue
-            r = pos % ring if ring else pos
+            r = g.place(pos)
             out.append(g.pages[s][r // P] * P + r % P)
         return out
 

@@ -2,7 +2,8 @@ from .base import (Architecture, ConfigError, ModelConfig, architecture_of, load
                    register_architecture, registered_architectures)
 from .banevik import BanevikConfig
 from .gemma2 import Gemma2Config
+from .kedasun import KedasunConfig
 from .neburax import NeburaxConfig
 
-__all__ = ["Architecture", "ConfigError", "ModelConfig", "Gemma2Config", "BanevikConfig", "NeburaxConfig", "architecture_of",
+__all__ = ["Architecture", "ConfigError", "ModelConfig", "Gemma2Config", "BanevikConfig", "NeburaxConfig", "KedasunConfig", "architecture_of",
            "load_config", "register_architecture", "registered_architectures"]

@@ -24,6 +24,15 @@
 // With a chunk size C (chunk > 0) a key must also lie in the query's own chunk: j >= p - p % C, chunks
 // counted from position 0 of the sequence.  Value rows may have a size of their own (vd), apart from
 // the size of query and key rows (hd).
+// Further options, each off by default.  A distance bias: slope[head] * (p - j) is taken off the scaled
+// score.  Kept first keys: with a window, key j < keep_first stays visible however far back it lies; in the
+// paged cache the first `ring_from` places are then held for good and the ring begins behind them (place of
+// position p: p below ring_from, else ring_from + (p - ring_from) % ring).  Values of all kv heads
+// (`v_all` > 0): a query head's weights are applied to the value rows of `v_all` kv heads from `v_from` on
+// at once; the output row of a head is [n_kv][vd] and a call fills its kv heads' part of it (a caller
+// whose n_kv * vd is beyond the kernel's row limit calls several times); what a mixing of the heads'
+// weights after the softmax needs.  A float
+// output whatever the element type of q, k and v (`out_f32`).
 #include "common.cuh"
 
 namespace {
@@ -56,7 +65,17 @@ struct AttnArgs {
     int chunk;                // > 0: keys before the start of the query's chunk are not visible
     int vec;                  // rows are read eight elements at a time (sizes and strides allow it); else one by one
     const float* sink;        // [n_kv * group] or null: exp(sink[head]) joins the softmax's denominator, with no value
+    const float* slopes;      // [n_kv * group] or null: slopes[head] * (position - key) is taken off the score
+    int keep_first;           // with a window: keys below this position stay visible
+    int ring_from;            // paged: places held for good ahead of the ring
+    int v_all;                // > 0: values of this many kv heads from v_from on; vd is then v_all * vd_head
+    int v_from;
+    int vd_head;              // a kv head's value size
+    int out_f32;              // the output is float whatever T is
 };
+
+// Place of position p in a sequence's pages: the first `from` places are held for good, the ring lies behind them.
+__device__ __forceinline__ int ring_place(int p, int from, int ring) { return p < from ? p : from + (p - from) % ring; }
 
 // DPL: output dims per lane = ceil(vd / 32) rounded up to the instantiated size.
 template <typename T, int DPL, bool PAGED>
@@ -110,21 +129,31 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
     int key_lo = max(0, pos_lo - window + 1);
     if (a.chunk > 0) key_lo = max(key_lo, pos_lo - pos_lo % a.chunk);
     const int key_hi = pos_hi;   // inclusive
+    // keys below `kept` are read as well, whatever the window says (each row's own mask decides)
+    const int kept = (a.keep_first > 0 && a.chunk <= 0) ? min(a.keep_first, key_lo) : 0;
+    const int vdh = a.v_all ? a.vd_head : vd;          // row size of the value store
+    const int out_head = a.v_all ? a.n_kv * vdh : vd;  // a head's row in the output, and where this call's part begins
+    const int out_from = a.v_all ? a.v_from * vdh : 0;
 
     // per-row state of this warp
     int rpos[RPW];
-    float m[RPW], l[RPW], acc[RPW][DPL];
+    float m[RPW], l[RPW], acc[RPW][DPL], slope[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         const int r = warp * RPW + i;
         rpos[i] = r < rows_here ? first_pos + (row0 + r) / a.group : -1;
+        slope[i] = (a.slopes && r < rows_here) ? a.slopes[g * a.group + (row0 + r) % a.group] : 0.0f;
         m[i] = -INFINITY;
         l[i] = 0.0f;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) acc[i][d] = 0.0f;
     }
 
-    for (int t0 = (key_lo / KT) * KT; t0 <= key_hi; t0 += KT) {
+    for (int t0 = kept > 0 ? 0 : (key_lo / KT) * KT; t0 <= key_hi; t0 += KT) {
+        if (t0 >= kept && t0 + KT <= key_lo) {        // between the kept first keys and the window: nothing to read
+            t0 = (key_lo / KT) * KT - KT;
+            continue;
+        }
         __syncthreads();   // the tile before this one is consumed (and Qs is written, first time)
         // stage keys and values t0 .. t0+KT-1; places outside [key_lo, key_hi] read as zero
         if (!a.vec) {
@@ -132,9 +161,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
                 const int j = idx / hd4, c = idx - j * hd4;
                 const int kp = t0 + j;
                 float v = 0.0f;
-                if (kp >= key_lo && kp <= key_hi && c < hd) {
+                if ((kp >= key_lo || kp < kept) && kp <= key_hi && c < hd) {
                     if (PAGED) {
-                        const int ridx = kp % a.ring;
+                        const int ridx = ring_place(kp, a.ring_from, a.ring);
                         const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
                         v = to_float(((const T*)a.k_pages)[(((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * hd + c]);
                     } else {
@@ -147,13 +176,14 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
                 const int j = idx / vd, c = idx - j * vd;
                 const int kp = t0 + j;
                 float v = 0.0f;
-                if (kp >= key_lo && kp <= key_hi) {
+                if ((kp >= key_lo || kp < kept) && kp <= key_hi) {
+                    const int vg = a.v_all ? a.v_from + c / vdh : g, vc = a.v_all ? c % vdh : c;
                     if (PAGED) {
-                        const int ridx = kp % a.ring;
+                        const int ridx = ring_place(kp, a.ring_from, a.ring);
                         const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
-                        v = to_float(((const T*)a.v_pages)[(((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * vd + c]);
+                        v = to_float(((const T*)a.v_pages)[(((size_t)page * a.n_kv + vg) * a.page_size + ridx % a.page_size) * vdh + vc]);
                     } else {
-                        v = to_float(((const T*)a.v)[(size_t)(q0 + kp) * a.v_stride + g * vd + c]);
+                        v = to_float(((const T*)a.v)[(size_t)(q0 + kp) * a.v_stride + vg * vdh + vc]);
                     }
                 }
                 Vs[j * vd + c] = v;
@@ -163,9 +193,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
             const int j = idx / (hd / 8), c = (idx - j * (hd / 8)) * 8;
             const int kp = t0 + j;
             float kv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (kp >= key_lo && kp <= key_hi) {
+            if ((kp >= key_lo || kp < kept) && kp <= key_hi) {
                 if (PAGED) {
-                    const int ridx = kp % a.ring;
+                    const int ridx = ring_place(kp, a.ring_from, a.ring);
                     const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
                     const size_t off = (((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * hd + c;
                     load8((const T*)a.k_pages + off, kv);
@@ -180,14 +210,15 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
             const int j = idx / (vd / 8), c = (idx - j * (vd / 8)) * 8;
             const int kp = t0 + j;
             float vv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (kp >= key_lo && kp <= key_hi) {
+            if ((kp >= key_lo || kp < kept) && kp <= key_hi) {
+                const int vg = a.v_all ? a.v_from + c / vdh : g, vc = a.v_all ? c % vdh : c;
                 if (PAGED) {
-                    const int ridx = kp % a.ring;
+                    const int ridx = ring_place(kp, a.ring_from, a.ring);
                     const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
-                    const size_t off = (((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * vd + c;
+                    const size_t off = (((size_t)page * a.n_kv + vg) * a.page_size + ridx % a.page_size) * vdh + vc;
                     load8((const T*)a.v_pages + off, vv);
                 } else {
-                    load8((const T*)a.v + (size_t)(q0 + kp) * a.v_stride + g * vd + c, vv);
+                    load8((const T*)a.v + (size_t)(q0 + kp) * a.v_stride + vg * vdh + vc, vv);
                 }
             }
 #pragma unroll
@@ -215,9 +246,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
         float p[RPW];
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
-            const bool visible = rpos[i] >= 0 && kp <= rpos[i] && rpos[i] - kp < window &&
+            const bool visible = rpos[i] >= 0 && kp <= rpos[i] && (rpos[i] - kp < window || kp < a.keep_first) &&
                                  (a.chunk <= 0 || kp >= rpos[i] - rpos[i] % a.chunk);
-            const float sc = visible ? soft_cap(s[i] * a.scale, a.cap) : -INFINITY;
+            float sc = visible ? soft_cap(s[i] * a.scale, a.cap) : -INFINITY;
+            if (visible && a.slopes) sc -= slope[i] * (float)(rpos[i] - kp);
             const float tile_max = warp_max(sc);
             const float m_new = fmaxf(m[i], tile_max);
             float corr = 1.0f;
@@ -257,7 +289,16 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
         float den = l[i];
         if (a.sink && m[i] > -INFINITY) den += expf(a.sink[head] - m[i]);
         const float inv = den > 0.0f ? 1.0f / den : 0.0f;
-        T* dst = og + (size_t)(q0 + tok) * a.out_stride + head * vd;
+        if (a.out_f32) {
+            float* dst = (float*)a.out + (size_t)(q0 + tok) * a.out_stride + (size_t)head * out_head + out_from;
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) {
+                const int dim = lane + 32 * d;
+                if (dim < vd) dst[dim] = acc[i][d] * inv;
+            }
+            continue;
+        }
+        T* dst = og + (size_t)(q0 + tok) * a.out_stride + (size_t)head * out_head + out_from;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) {
             const int dim = lane + 32 * d;
@@ -307,15 +348,21 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
                               const void* kv_len, const void* k, const void* v, int kv_stride, const void* k_pages,
                               const void* v_pages, const void* page_table, int pt_stride, int ring, int page_size,
                               int n_kv, int group, int hd, float scale, float cap, int window, const void* sink,
-                              int batch, int max_q_len, int vd, int v_stride, int chunk, cudaStream_t stream) {
+                              int batch, int max_q_len, int vd, int v_stride, int chunk, const void* slopes,
+                              int keep_first, int ring_from, int v_all, int v_from, int out_f32, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     if (hd <= 0 || hd > 512 || group <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
+    const int vd_head = vd;
+    if (v_all < 0 || v_from < 0 || v_from + v_all > n_kv) return BROLM_ERR_BAD_SIZE;
+    if (v_all) vd = vd * v_all;                        // a head's output row holds the values of several kv heads
     if (vd <= 0 || vd > 512) return BROLM_ERR_BAD_SIZE;
-    bool vec = hd % 8 == 0 && vd % 8 == 0 && q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0;
+    if (keep_first < 0 || ring_from < 0 || (keep_first > 0 && chunk > 0)) return BROLM_ERR_BAD_SIZE;
+    bool vec = hd % 8 == 0 && vd_head % 8 == 0 && q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0;
     if (batch > 65535 || n_kv > 65535) return BROLM_ERR_TOO_LARGE;
     const bool paged = k_pages != nullptr;
     if (paged) {
         if (ring <= 0 || page_size <= 0 || page_size % KT != 0 || ring % page_size != 0) return BROLM_ERR_BAD_SIZE;
+        if (ring_from % page_size != 0 || ring_from < keep_first) return BROLM_ERR_BAD_SIZE;
     } else {
         if (!k || !v) return BROLM_ERR_ALIGNMENT;
         vec = vec && kv_stride % 8 == 0 && v_stride % 8 == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0;
@@ -327,6 +374,8 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
     a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = (const int32_t*)page_table;
     a.pt_stride = pt_stride; a.ring = ring; a.page_size = page_size;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.sink = (const float*)sink;
+    a.slopes = (const float*)slopes; a.keep_first = window > 0 ? keep_first : 0; a.ring_from = ring_from; a.v_all = v_all; a.v_from = v_from;
+    a.vd_head = vd_head; a.out_f32 = out_f32 ? 1 : 0;
     if (dtype == BROLM_F32) return dispatch<float>(a, paged, batch, max_q_len, stream);
     if (dtype == BROLM_BF16) return dispatch<bf16>(a, paged, batch, max_q_len, stream);
     return BROLM_ERR_BAD_DTYPE;

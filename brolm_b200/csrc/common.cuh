@@ -119,6 +119,15 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
     }
 }
 
+// A gate that is clamped from above and a partner that is clamped on both sides and shifted by one:
+//     g' = min(g, limit),  u' = clamp(u, -limit, limit),  g' * sigmoid(1.702 g') * (u' + 1)
+// (activation code 2 of the gated feed-forward; codes 0 and 1 are act(g) * u with gelu and silu).
+__device__ __forceinline__ float clamped_gate(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
 static inline int launch_status() {
     return (int)cudaGetLastError();
 }

@@ -781,6 +781,7 @@ BROLM_API int brolm_rope_kv_write(void* qkv, int dtype, const void* positions, c
 //     out[t, j] = act(gate[t, j]) * up[t, j]        (src/gemma2.cpp:380-381)
 // act 0: gelu, tanh form  0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 // act 1: silu             z / (1 + exp(-z))
+// act 2: the clamped gate of common.cuh, a function of gate, up and a limit
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float act_apply(float z, int act) {
     if (act == 0) {
@@ -791,18 +792,19 @@ __device__ __forceinline__ float act_apply(float z, int act) {
 }
 
 template <typename T>
-__global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int act) {
+__global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int act, float limit) {
     const size_t t = blockIdx.x;
     const T* g = gate_up + t * 2 * (size_t)inter;
     const T* u = g + inter;
     T* o = out + t * (size_t)inter;
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < inter; j += gridDim.y * blockDim.x)
-        o[j] = from_float<T>(act_apply(to_float(g[j]), act) * to_float(u[j]));
+        o[j] = from_float<T>(act == 2 ? clamped_gate(to_float(g[j]), to_float(u[j]), limit)
+                                      : act_apply(to_float(g[j]), act) * to_float(u[j]));
 }
 
 // bfloat16 with inter a multiple of 8: eight elements per thread, 16-byte accesses.
 __global__ void __launch_bounds__(256) gated_act_vec_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out,
-                                                            int inter, int act) {
+                                                            int inter, int act, float limit) {
     const size_t t = blockIdx.x;
     const bf16* g = gate_up + t * 2 * (size_t)inter;
     const bf16* u = g + inter;
@@ -815,28 +817,31 @@ __global__ void __launch_bounds__(256) gated_act_vec_kernel(const bf16* __restri
         __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-            r2[e] = __floats2bfloat162_rn(act_apply(gv[2 * e], act) * uv[2 * e], act_apply(gv[2 * e + 1], act) * uv[2 * e + 1]);
+            r2[e] = act == 2 ? __floats2bfloat162_rn(clamped_gate(gv[2 * e], uv[2 * e], limit),
+                                                     clamped_gate(gv[2 * e + 1], uv[2 * e + 1], limit))
+                             : __floats2bfloat162_rn(act_apply(gv[2 * e], act) * uv[2 * e],
+                                                     act_apply(gv[2 * e + 1], act) * uv[2 * e + 1]);
         *reinterpret_cast<uint4*>(o + j) = r;
     }
 }
 
-BROLM_API int brolm_gated_act(const void* gate_up, void* out, int dtype, int tokens, int inter, int act,
+BROLM_API int brolm_gated_act(const void* gate_up, void* out, int dtype, int tokens, int inter, int act, float limit,
                               cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
-    if (act < 0 || act > 1) return BROLM_ERR_BAD_SIZE;
+    if (act < 0 || act > 2) return BROLM_ERR_BAD_SIZE;
     if (dtype == BROLM_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         int by = (inter / 8 + 255) / 256;
         if (by > 65535) by = 65535;
-        gated_act_vec_kernel<<<dim3(tokens, by), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, act);
+        gated_act_vec_kernel<<<dim3(tokens, by), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, act, limit);
         return launch_status();
     }
     int by = (inter + 1023) / 1024;
     if (by > 65535) by = 65535;
     dim3 grid(tokens, by);
     if (dtype == BROLM_F32)
-        gated_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, act);
+        gated_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, act, limit);
     else if (dtype == BROLM_BF16)
-        gated_act_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, act);
+        gated_act_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, act, limit);
     else
         return BROLM_ERR_BAD_DTYPE;
     return launch_status();

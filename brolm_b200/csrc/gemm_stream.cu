@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(const __grid_co
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (quarter < 2) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = fast_gate_act(o[i], g.act) * upx[lrow * BT + c + i];
+                        for (int i = 0; i < 16; ++i) o[i] = fast_gate_pair(o[i], upx[lrow * BT + c + i], g.act, g.cap);   // code 2: cap is its limit
                     }
                     writer = quarter < 2;
                     asm volatile("bar.sync 1, 128;" ::: "memory");          // upx may be written again
@@ -296,7 +296,7 @@ BROLM_API int brolm_gemm_stream(const void* x, int ldx, const void* w, int ldw, 
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return BROLM_ERR_ALIGNMENT;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return BROLM_ERR_ALIGNMENT;
     if (epilogue < 0 || epilogue > 2) return BROLM_ERR_BAD_SIZE;
-    if (epilogue == EPI_GATED && (N % 64 != 0 || act < 0 || act > 1)) return BROLM_ERR_BAD_SIZE;
+    if (epilogue == EPI_GATED && (N % 64 != 0 || act < 0 || act > 2)) return BROLM_ERR_BAD_SIZE;
     const int nkb = (K + BK - 1) / BK;
     if (ksplit < 1 || ksplit > nkb || (ksplit > 1 && epilogue != EPI_STORE)) return BROLM_ERR_BAD_SIZE;
     const int bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;

@@ -36,6 +36,7 @@ struct GemmArgs {
     int M, N, K;          // N: output columns (EPI_GATED: W has 2N rows)
     int out_f32;
     int act;
+    float limit;          // of activation code 2
     int m_tiles, n_tiles;
 };
 
@@ -202,7 +203,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     o[i] = __uint_as_float(v[i]);
-                    if (EPI == EPI_GATED) o[i] = fast_gate_act(o[i], g.act) * __uint_as_float(u[i]);
+                    if (EPI == EPI_GATED) o[i] = fast_gate_pair(o[i], __uint_as_float(u[i]), g.act, g.limit);
                 }
                 if (row < g.M) {
                     const int col = col0 + c;
@@ -260,11 +261,11 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& g, cuda
 
 // The arguments of brolm_gemm_tc.
 BROLM_API int brolm_gemm_tc2(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
-                             int epilogue, int out_f32, int act, cudaStream_t stream) {
+                             int epilogue, int out_f32, int act, float limit, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return BROLM_OK;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return BROLM_ERR_ALIGNMENT;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)y & 15)) return BROLM_ERR_ALIGNMENT;
-    if (epilogue == EPI_GATED && (N % 128 != 0 || act < 0 || act > 1)) return BROLM_ERR_BAD_SIZE;
+    if (epilogue == EPI_GATED && (N % 128 != 0 || act < 0 || act > 2)) return BROLM_ERR_BAD_SIZE;
     if (epilogue != EPI_STORE && epilogue != EPI_GATED) return BROLM_ERR_BAD_SIZE;
     CUtensorMap mx, mw;
     int st = make_map_2d(&mx, x, M, K, ldx, BM);
@@ -272,7 +273,7 @@ BROLM_API int brolm_gemm_tc2(const void* x, int ldx, const void* w, int ldw, voi
     st = make_map_2d(&mw, w, epilogue == EPI_GATED ? 2LL * N : N, K, ldw, HN);
     if (st) return st;
     GemmArgs g;
-    g.y = y; g.ldy = ldy; g.M = M; g.N = N; g.K = K; g.out_f32 = out_f32; g.act = act;
+    g.y = y; g.ldy = ldy; g.M = M; g.N = N; g.K = K; g.out_f32 = out_f32; g.act = act; g.limit = limit;
     g.m_tiles = (M + PM - 1) / PM;
     const int out_cols = epilogue == EPI_GATED ? BN / 2 : BN;
     g.n_tiles = (N + out_cols - 1) / out_cols;

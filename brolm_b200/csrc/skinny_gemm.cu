@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_kernel(SkinnyArgs a) {
                 gsum += red[w][((2 * ot) * NT + j) * 4 + e][ln];
                 usum += red[w][((2 * ot + 1) * NT + j) * 4 + e][ln];
             }
-            v = act_apply(gsum, a.act) * usum;
+            v = a.act == 2 ? clamped_gate(gsum, usum, a.cap) : act_apply(gsum, a.act) * usum;   // code 2: cap is its limit
         } else {
             v = 0.0f;
 #pragma unroll
@@ -374,7 +374,7 @@ BROLM_API int brolm_skinny_gemm(const void* x, int ldx, const void* w, int ldw, 
     if (M > 16) return BROLM_ERR_TOO_LARGE;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return BROLM_ERR_ALIGNMENT;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return BROLM_ERR_ALIGNMENT;
-    if (epilogue == EPI_GATED && (act < 0 || act > 1)) return BROLM_ERR_BAD_SIZE;
+    if (epilogue == EPI_GATED && (act < 0 || act > 2)) return BROLM_ERR_BAD_SIZE;
     SkinnyArgs a;
     a.x = (const bf16*)x; a.w = (const bf16*)w; a.y = y; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
     a.M = M; a.N = N; a.K = K; a.out_f32 = out_f32; a.act = act; a.cap = cap;

@@ -185,6 +185,16 @@ __device__ __forceinline__ float fast_gate_act(float z, int act) {
     return z * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * k));
 }
 
+// The gated pair of an epilogue: act(z) * u for codes 0 and 1, the clamped gate of common.cuh for code 2.
+__device__ __forceinline__ float fast_gate_pair(float z, float u, int act, float limit) {
+    if (act == 2) {
+        z = fminf(z, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        return z * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * 1.702f * z)) * u;
+    }
+    return fast_gate_act(z, act) * u;
+}
+
 // ---- host: tensor maps (the driver's encoder is fetched through the runtime, nothing links to libcuda)
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -38,6 +38,9 @@ class StepContext:
     host_lengths: list             # host copy of kv_len
     max_kv_len: int = 0            # an upper bound of kv_len for sizing launches (a captured graph fixes it)
     ragged: bool = False           # decode: the lengths are far from equal (a hint for how attention cuts its work)
+    # what one layer of a pass leaves for later layers of the same pass (by name; the model empties it
+    # at the start of every pass): values that belong to the step's tokens, never to a sequence
+    carry: dict = dataclasses.field(default_factory=dict)
 
     def __post_init__(self):
         if not self.max_kv_len:
@@ -47,6 +50,10 @@ class StepContext:
         """(k_pages, v_pages, page_table, ring, page_size) of a key/value entry."""
         g: KVGroup = entry.group
         return entry.k, entry.v, self.page_tables[entry.group_id], g.ring_tokens, g.page_size
+
+    def ring_from(self, entry: CacheEntry) -> int:
+        """How many places ahead of the ring a key/value entry holds for good (0: none)."""
+        return entry.group.head
 
     def state(self, entry: CacheEntry) -> torch.Tensor:
         """[max_slots + 1, *shape] state tensor of a state entry; index it with ``slots_dev``

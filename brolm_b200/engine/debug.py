@@ -70,7 +70,7 @@ def check_step(cache, mode: str, vocab: int, tokens: Optional[np.ndarray], slots
             fail(f"group {g}: a page table entry is outside the pool of {pool_pages} pages")
         seen: dict[int, int] = {}
         for r in np.flatnonzero(live_row):
-            keys = int(kv_len[r]) if not grp.ring else min(int(kv_len[r]), grp.ring)
+            keys = int(kv_len[r]) if not grp.ring else min(int(kv_len[r]), grp.head + grp.ring)
             need = (keys + P - 1) // P
             if need > table.shape[1]:
                 fail(f"group {g}, row {r}: {need} pages are needed and the table is {table.shape[1]} wide")
@@ -92,12 +92,12 @@ def check_step(cache, mode: str, vocab: int, tokens: Optional[np.ndarray], slots
         for t in np.flatnonzero(kept):
             r = int(tok_seq[t])
             pos = int(positions[t])
-            place = pos % grp.ring if grp.ring else pos
+            place = int(grp.place(pos))
             want = cache.kv_groups[g].pages[slots[r]][place // P] * P + place % P
             if int(crow[t]) != want:
                 fail(f"group {g}, token {t}: cache row {int(crow[t])}, but position {pos} of slot {slots[r]} lives at {want}")
         # a token that is not kept must be one that a later token of the same step overwrites in the ring
         for t in np.flatnonzero(live_tok & (crow < 0)):
             r = int(tok_seq[t])
-            if not grp.ring or int(positions[t]) + grp.ring >= int(kv_len[r]):
+            if not grp.ring or int(positions[t]) + grp.ring >= int(kv_len[r]) or int(positions[t]) < grp.head:
                 fail(f"group {g}, token {t}: not kept, although nothing of this step takes its place")

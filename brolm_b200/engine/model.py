@@ -93,6 +93,8 @@ class DecoderModel:
         head = self.layout.head
         if head.tensor not in out:
             out[head.tensor] = Expected((emb.vocab, emb.hidden), "matrix", optional=head.tied_to is not None)
+        for name, shape in self.layout.unused_tensors.items():
+            out.setdefault(name, Expected(tuple(shape), "vector", optional=True))
         return out
 
     # weights --------------------------------------------------------------
@@ -159,6 +161,7 @@ class DecoderModel:
         if not self.loaded:
             raise RuntimeError("forward: weights not loaded")
         lay = self.layout
+        ctx.carry.clear()
         h = torch.empty((ctx.n_tokens, lay.embedding.hidden), dtype=torch.float32, device=self.device)
         emb = lay.embedding
         if emb.pairs is not None:

@@ -74,7 +74,7 @@ class _DecodeGraph:
         for g in cache.kv_groups:
             w = (cache.max_positions + g.page_size - 1) // g.page_size
             if g.ring:
-                w = min(w, g.ring // g.page_size)
+                w = min(w, (g.head + g.ring) // g.page_size)
             self.widths.append(max(1, w))
         n = 4 * rows + sum(rows * w for w in self.widths) + rows * len(self.widths)
         self.pick_off = n                    # last: which element of a tensor of drawn ids each row's token is

@@ -23,7 +23,9 @@ _ERRORS = {
     10003: "a size beyond the kernel's limit",
     10004: "a stride or pointer that is not aligned as the kernel needs",
 }
-ACTIVATIONS = {"gelu_tanh": 0, "gelu_pytorch_tanh": 0, "silu": 1}
+# gated activations: act(gate) * up for the first two; "clamped_gate" is min(g, limit) * sigmoid(1.702 min(g, limit))
+# * (clamp(up, -limit, limit) + 1) and takes ``limit`` wherever an activation is named
+ACTIVATIONS = {"gelu_tanh": 0, "gelu_pytorch_tanh": 0, "silu": 1, "clamped_gate": 2}
 
 
 class KernelError(RuntimeError):
@@ -209,14 +211,14 @@ def rope_kv_write_parts(parts: torch.Tensor, qkv: torch.Tensor, positions: torch
              page_size, qkv.shape[0], _stream()), "rope_kv_write_parts")
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """out = act(gate) * up for gate_up = [gate | up] (tokens, 2 * inter)."""
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0) -> None:
+    """out = act(gate) * up for gate_up = [gate | up] (tokens, 2 * inter); ``limit`` for "clamped_gate"."""
     assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
     assert gate_up.shape[1] == 2 * out.shape[1] and gate_up.shape[0] == out.shape[0]
     if activation not in ACTIVATIONS:
         raise KernelError(f"gated_act: unknown activation '{activation}' (known: {sorted(ACTIVATIONS)})")
-    f = _fn("core", "brolm_gated_act", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(gate_up), _ptr(out), _code(out), out.shape[0], out.shape[1], ACTIVATIONS[activation], _stream()),
+    f = _fn("core", "brolm_gated_act", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _code(out), out.shape[0], out.shape[1], ACTIVATIONS[activation], limit, _stream()),
            "gated_act")
 
 
@@ -516,6 +518,119 @@ def qkv_norm_write(proj: torch.Tensor, q_cols: int, k_cols: int, v_cols: int, q_
              proj.shape[0], _stream()), "qkv_norm_write")
 
 
+ROPE_PAIRINGS = {"half": 0, "interleaved": 1}
+
+
+def qkv_finish(proj: torch.Tensor, bias: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, v_dim: int,
+               positions: torch.Tensor, out: torch.Tensor, *, head_norm: bool = False, eps: float = 0.0,
+               cos_sin: Optional[torch.Tensor] = None, rotary_dim: int = 0, pairing: str = "half",
+               mix: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None,
+               v_keep: Optional[torch.Tensor] = None, k_pages: Optional[torch.Tensor] = None,
+               v_pages: Optional[torch.Tensor] = None, cache_rows: Optional[torch.Tensor] = None,
+               page_size: int = 64) -> None:
+    """A projection's rows [q: n_q * head_dim | k: n_kv * head_dim | v: n_kv * v_dim] made ready for attention:
+    ``proj`` (tokens, cols) or float32 partial sums [parts, tokens, cols] plus ``bias`` (float32 [cols]); every q
+    and k head divided by its root mean square (``head_norm``, no gain); the first ``rotary_dim`` elements of
+    every q and k head rotated with ``cos_sin`` [positions, rotary_dim / 2, 2], pairs (i, i + rotary_dim / 2)
+    ("half") or (2i, 2i + 1) ("interleaved"); v <- (1 - mix) v + mix v_first with ``mix`` a float32 scalar on
+    the device and ``v_first`` float32 (tokens, n_kv * v_dim); ``v_keep`` (float32, contiguous) takes this layer's
+    own values as they are before the mixing; the result in ``out``'s element type into ``out`` and the cache."""
+    cols = (n_q + n_kv) * head_dim + n_kv * v_dim
+    parts, part_stride = (proj.shape[0], proj.stride(0)) if proj.dim() == 3 else (1, 0)
+    assert proj.shape[-1] == cols and proj.stride(-1) == 1 and out.stride(1) == 1 and out.shape == (proj.shape[-2], cols)
+    assert parts == 1 or proj.dtype == torch.float32
+    assert positions.dtype == torch.int32 and positions.numel() == out.shape[0]
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == cols)
+    if pairing not in ROPE_PAIRINGS:
+        raise KernelError(f"qkv_finish: unknown pairing '{pairing}' (known: {sorted(ROPE_PAIRINGS)})")
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (rotary_dim // 2, 2)
+        assert 0 < rotary_dim <= head_dim and rotary_dim % 2 == 0
+    ld_first = 0
+    if v_first is not None:
+        assert mix is not None and mix.dtype == torch.float32 and mix.numel() == 1
+        assert v_first.dtype == torch.float32 and v_first.stride(1) == 1 and v_first.shape == (out.shape[0], n_kv * v_dim)
+        ld_first = v_first.stride(0)
+    if v_keep is not None:
+        assert v_keep.dtype == torch.float32 and v_keep.is_contiguous() and v_keep.shape == (out.shape[0], n_kv * v_dim)
+    if k_pages is not None:
+        assert v_pages is not None and cache_rows is not None and k_pages.dtype == out.dtype and v_pages.dtype == out.dtype
+        assert k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
+        assert tuple(v_pages.shape[1:]) == (n_kv, page_size, v_dim)
+        assert cache_rows.dtype == torch.int32 and cache_rows.numel() == out.shape[0]
+    f = _fn("headwise", "brolm_qkv_finish", [c_void_p, c_int, c_int, c_longlong, c_long, c_void_p, c_int, c_int, c_int,
+                                             c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                             c_long, c_void_p, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p,
+                                             c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), _code(proj), parts, part_stride, proj.stride(-2), _ptr(bias), n_q, n_kv, head_dim, v_dim,
+             1 if head_norm else 0, eps, _ptr(positions), _ptr(cos_sin), rotary_dim, ROPE_PAIRINGS[pairing],
+             _ptr(mix) if v_first is not None else None, _ptr(v_first), ld_first, _ptr(v_keep), _ptr(out), _code(out),
+             out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows) if k_pages is not None else None, page_size,
+             out.shape[0], _stream()), "qkv_finish")
+
+
+def heads_mix(acc: torch.Tensor, talk: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
+              heads: int, n_kv: int, v_dim: int) -> None:
+    """out[t, h] = sigmoid(gate[t, h]) * sum_g talk[h, g] * acc[t, g, kv head of h]: ``acc`` float32
+    (tokens, heads * n_kv * v_dim) holds every head's weights applied to the values of every kv head, ``talk``
+    float32 [heads, heads] mixes the heads' weights, ``gate`` float32 (tokens, heads) logits or None.
+    Without ``talk`` acc is (tokens, heads * v_dim), every head's own result, and only the gate is applied."""
+    assert acc.dtype == torch.float32 and acc.stride(1) == 1
+    assert acc.shape[1] == heads * v_dim * (n_kv if talk is not None else 1)
+    assert talk is None or (talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (heads, heads))
+    assert out.stride(1) == 1 and out.shape == (acc.shape[0], heads * v_dim)
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (acc.shape[0], heads)
+    f = _fn("headwise", "brolm_heads_mix", [c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_int, c_long, c_int,
+                                            c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(acc), acc.stride(0), _ptr(talk), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+             _code(out), out.stride(0), heads, n_kv, v_dim, acc.shape[0], _stream()), "heads_mix")
+
+
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, groups: int, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows[r] or r], every one of ``groups`` equal consecutive parts of the row divided by its own
+    sqrt(mean(part^2) + eps), the whole times (offset + weight)."""
+    assert x.is_contiguous() and out.is_contiguous() and weight.is_contiguous()
+    n, hidden = out.shape[0], x.shape[-1]
+    assert weight.numel() == hidden and out.shape[-1] == hidden and hidden % groups == 0
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n
+    else:
+        assert x.shape[0] == n
+    f = _fn("groupnorm", "brolm_group_rmsnorm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p,
+                                                 c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _code(x), _ptr(rows), _ptr(weight), _code(weight), eps, offset, _ptr(out), _code(out), n, hidden,
+             groups, _stream()), "group_rmsnorm")
+
+
+def residual_group_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[torch.Tensor], post_eps: float,
+                           post_offset: float, next_weight: Optional[torch.Tensor], next_eps: float, next_offset: float,
+                           groups: int, out: Optional[torch.Tensor]) -> None:
+    """``residual_rmsnorm`` with both norms taken in ``groups`` equal consecutive parts of the row."""
+    assert h.dtype == torch.float32 and h.is_contiguous() and y.is_contiguous() and tuple(y.shape[-2:]) == tuple(h.shape)
+    n_parts, part_stride = (y.shape[0], y.stride(0)) if y.dim() == 3 else (1, 0)
+    wd = None
+    for w in (post_weight, next_weight):
+        if w is not None:
+            assert w.is_contiguous() and w.numel() == h.shape[-1]
+            if wd is not None and w.dtype != wd:
+                raise KernelError("residual_group_rmsnorm: both gains must have one element type")
+            wd = w.dtype
+    if next_weight is not None:
+        assert out is not None
+    if out is not None:
+        assert out.is_contiguous() and out.shape == h.shape
+    f = _fn("groupnorm", "brolm_residual_group_rmsnorm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float,
+                                                          c_float, c_void_p, c_float, c_float, c_int, c_void_p, c_int,
+                                                          c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(y), _code(y), n_parts, part_stride, _ptr(post_weight), post_eps, post_offset,
+             _ptr(next_weight), next_eps, next_offset, _CODES[wd] if wd is not None else F32,
+             _ptr(out) if out is not None else None, _code(out) if out is not None else F32, h.shape[0], h.shape[-1],
+             groups, _stream()), "residual_group_rmsnorm")
+
+
 def gate_group_norm(y: torch.Tensor, z: torch.Tensor, gain: torch.Tensor, eps: float, groups: int,
                     out: torch.Tensor) -> None:
     """out = rmsnorm over each of ``groups`` equal parts of (y * silu(z)), times gain.  y float32 (tokens, n);
@@ -764,7 +879,7 @@ def skinny_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] = Non
 
 
 def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
-                activation: str = "gelu_tanh", cap: float = 0.0) -> None:
+                activation: str = "gelu_tanh", cap: float = 0.0, limit: float = 0.0) -> None:
     """out = x @ weight^T for at most 16 rows of x (bfloat16 in, float32 accumulation).
 
     ``epilogue``: "store" (out bfloat16 or float32), "gated" (weight = [Wg; Wu],
@@ -795,8 +910,8 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
                                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_longlong,
                                                  c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
-             1 if out.dtype == torch.float32 else 0, ACTIVATIONS.get(activation, 0), cap, tiles, ksplit, part_stride,
-             _stream()), "skinny_gemm")
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS.get(activation, 0), limit if code == 1 else cap, tiles,
+             ksplit, part_stride, _stream()), "skinny_gemm")
 
 
 def skinny_qkv_rope(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
@@ -844,7 +959,7 @@ def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, gated: bool = False, sms: 
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
-            activation: str = "gelu_tanh", pairs: Optional[bool] = None) -> None:
+            activation: str = "gelu_tanh", pairs: Optional[bool] = None, limit: float = 0.0) -> None:
     """out = x @ weight^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulation in tensor memory).
 
     Runs on pairs of SMs (``gemm_tc2``: 256 x 256 tiles, tcgen05 cta_group::2) unless ``pairs`` is False or
@@ -860,15 +975,15 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
     if activation not in ACTIVATIONS:
         raise KernelError(f"gemm_tc: unknown activation '{activation}'")
     if USE_PAIR_GEMM and pairs is not False:
-        return gemm_tc2(x, weight, out, epilogue, activation)
+        return gemm_tc2(x, weight, out, epilogue, activation, limit)
     f = _fn("gemm_tc", "brolm_gemm_tc", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                         c_int, c_int, c_void_p])
+                                         c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
-             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], _stream()), "gemm_tc")
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], limit, _stream()), "gemm_tc")
 
 
 def gemm_tc2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
-             activation: str = "gelu_tanh") -> None:
+             activation: str = "gelu_tanh", limit: float = 0.0) -> None:
     """``gemm_tc`` on pairs of SMs (tcgen05 cta_group::2): 256 x 256 tiles, each block of a pair loads half
     of the weight tile.  Same operands and epilogues."""
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
@@ -878,9 +993,9 @@ def gemm_tc2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue:
     N = out.shape[1]
     assert weight.shape == ((2 * N if code == 1 else N), K)
     f = _fn("gemm_tc2", "brolm_gemm_tc2", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                           c_int, c_int, c_void_p])
+                                           c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
-             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], _stream()), "gemm_tc2")
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], limit, _stream()), "gemm_tc2")
 
 
 def gemm_tc2_status(reset: bool = False) -> int:
@@ -960,7 +1075,7 @@ def gemm_stream_parts(x: torch.Tensor, weight: torch.Tensor, sms: Optional[int] 
 
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "store",
-                activation: str = "gelu_tanh", cap: float = 0.0) -> None:
+                activation: str = "gelu_tanh", cap: float = 0.0, limit: float = 0.0) -> None:
     """out = x @ weight^T for at most 128 rows of x on tcgen05, the weights streamed through a TMA ring.
 
     ``epilogue``: "store" (out bfloat16 or float32, or [parts, M, N] float32 partial sums of K slices),
@@ -981,8 +1096,8 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
     f = _fn("gemm_stream", "brolm_gemm_stream", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
-             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], cap, ksplit, part_stride, _stream()),
-           "gemm_stream")
+             1 if out.dtype == torch.float32 else 0, ACTIVATIONS[activation], limit if code == 1 else cap, ksplit,
+             part_stride, _stream()), "gemm_stream")
 
 
 def gemm_stream_status(reset: bool = False) -> int:
@@ -1000,14 +1115,25 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
                    k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
                    k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                    page_table: Optional[torch.Tensor] = None, ring: int = 0, page_size: int = 0,
-                   sink: Optional[torch.Tensor] = None, v_dim: Optional[int] = None, chunk: int = 0) -> None:
+                   sink: Optional[torch.Tensor] = None, v_dim: Optional[int] = None, chunk: int = 0,
+                   slopes: Optional[torch.Tensor] = None, keep_first: int = 0, ring_from: int = 0,
+                   v_all: int = 0, v_from: int = 0) -> None:
     """Exact attention on CUDA cores.  Keys come from (k, v) packed like q, or from cache pages.
     ``sink``: float32 [query heads]; exp(sink) joins every softmax's denominator (a key with no value).
     ``v_dim``: size of a value row and of an output row when it is not ``head_dim``.
-    ``chunk`` > 0: a query at position p sees no key before p - p % chunk."""
+    ``chunk`` > 0: a query at position p sees no key before p - p % chunk.
+    ``slopes``: float32 [query heads]; slopes[h] * (p - j) is taken off the scaled score of key j.
+    ``keep_first``: with a window, keys at positions below it stay visible; the pages then hold the first
+    ``ring_from`` places (a multiple of the page size, at least keep_first) for good, the ring behind them.
+    ``v_all`` > 0: every query head's weights are applied to the value rows of ``v_all`` kv heads from
+    ``v_from`` on; ``out`` is then (tokens, heads * n_kv * v_dim), head h's row being [n_kv][v_dim], of which
+    the call fills those kv heads' part (``attention_all_values`` covers all of them).
+    ``out`` may be float32 whatever the element type of q."""
     _check_sink(sink, n_kv * group)
+    _check_sink(slopes, n_kv * group)
     vd = v_dim or head_dim
-    assert q.stride(-1) == 1 and out.stride(-1) == 1 and q.dtype == out.dtype
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and (q.dtype == out.dtype or out.dtype == torch.float32)
+    assert out.shape[-1] >= n_kv * group * vd * (n_kv if v_all else 1) and 0 <= v_from <= n_kv - v_all
     assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
     kv_stride = v_stride = pt_stride = 0
     if k_pages is not None:
@@ -1023,11 +1149,27 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
     f = _fn("attn_simt", "brolm_attn_simt", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int,
-                                             c_int, c_int, c_int, c_void_p])
+                                             c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_code(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k), _ptr(v),
              kv_stride, _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, ring, page_size, n_kv, group,
-             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, vd, v_stride, int(chunk), _stream()),
+             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, vd, v_stride, int(chunk), _ptr(slopes),
+             int(keep_first), int(ring_from), int(v_all), int(v_from), 1 if out.dtype == torch.float32 else 0, _stream()),
            "attention_simt")
+
+
+ALL_VALUES_ROW = 512        # the exact kernel's limit for an output row of one head
+
+
+def attention_all_values(q: torch.Tensor, acc: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, *, n_kv: int,
+                         v_dim: int, **args) -> None:
+    """``attention_simt`` with every query head's weights applied to the values of every kv head: ``acc`` float32
+    (tokens, heads * n_kv * v_dim).  As many kv heads a call as fit the kernel's row; the scores are computed anew
+    by each call, in the same order, so the weights of all calls are the same bits."""
+    assert acc.dtype == torch.float32
+    per_call = max(1, min(n_kv, ALL_VALUES_ROW // v_dim))
+    for first in range(0, n_kv, per_call):
+        attention_simt(q, acc, cu_q, kv_len, n_kv=n_kv, v_dim=v_dim, v_all=min(per_call, n_kv - first), v_from=first,
+                       **args)
 
 
 def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:

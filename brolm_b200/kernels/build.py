@@ -46,6 +46,8 @@ LIBRARIES: dict[str, list[str]] = {
     "grouped_tc": ["grouped_tc.cu"],
     "rowwise": ["rowwise.cu"],
     "recurrent": ["recurrent.cu"],
+    "headwise": ["headwise.cu"],
+    "groupnorm": ["groupnorm.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
 

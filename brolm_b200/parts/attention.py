@@ -16,6 +16,34 @@ and j >= p - p % C, chunks counted from position 0), kept in the cache as a
 ring of C places like a window.  A layer that uses one of them runs its
 projection with a float result, the row-wise kernel that norms and fills the
 cache, and the exact attention kernel.
+
+A third set of options works one head at a time between the projection and
+the attention (``headwise``; the notation: H query heads, G key/value heads,
+head h reads kv head h // (H / G)):
+
+* ``bias``: q, k, v and the output projection have a bias each;
+* ``taps`` = K > 0: a causal convolution per channel over time on the projected
+  q, k and v (``y_t = sum_j w[:, j] u_(t - K + 1 + j)``, zeros before the
+  sequence's start), whose last K - 1 inputs are kept per sequence in a state
+  entry beside the keys and values;
+* ``qk_norm="head"``: every q and k head divided by its own root mean square
+  (``eps``), no gain;
+* a rotation of part of a head, in either pairing, also with ``v_dim``;
+* ``slope_power`` = s > 0: slope_h * (p - j) is taken off the scaled score of
+  key j at query position p, slope_h = 2^(-s (h + 1) / H);
+* ``keep_first`` = F with a window: keys at positions below F stay visible
+  however far back they lie, at their true positions;
+* ``talk``: the heads' softmax weights are mixed by an H x H matrix before they
+  meet the values, w'_h = sum_g talk[h, g] w_g, head h applying w'_h to the
+  values of its own kv head.  The attention kernel applies every head's
+  weights to the values of every kv head (float results [H, G, v_dim]) and a
+  row-wise kernel takes the sums over g;
+* ``gate``: head h's result is multiplied by sigmoid(W_g x)_h, W_g being H rows
+  of the fused projection;
+* ``v_mix``: "source" leaves the layer's values of the step's tokens (float,
+  before rounding) under ``v_mix_key`` for later layers of the same pass;
+  "mixed" makes v <- (1 - lambda) v + lambda v_source with a learned scalar
+  lambda, and that is what the cache keeps.  Both hold a tensor ``vmix``.
 """
 from __future__ import annotations
 
@@ -24,7 +52,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from ..cache import KVSpec
+from ..cache import KVSpec, StateSpec
 from .base import ParamSpec, Part, register_part
 from .linear import linear
 
@@ -35,16 +63,31 @@ class Attention(Part):
 
     def __init__(self, hidden: int, n_q: int, n_kv: int, head_dim: int, scale: float, softcap: float = 0.0,
                  window: Optional[int] = None, position: Optional[Part] = None, v_dim: Optional[int] = None,
-                 qk_norm: str = "none", eps: float = 0.0, chunk: Optional[int] = None):
+                 qk_norm: str = "none", eps: float = 0.0, chunk: Optional[int] = None, bias: bool = False, taps: int = 0,
+                 slope_power: float = 0.0, keep_first: int = 0, talk: bool = False, gate: bool = False,
+                 v_mix: Optional[str] = None, v_mix_key: str = "v_first"):
         if n_q % n_kv:
             raise ValueError("attention: the number of query heads must be a multiple of the kv heads")
-        plain = not (v_dim and v_dim != head_dim) and qk_norm == "none" and not chunk
+        rotation = getattr(position, "pairing", "half")
+        self.headwise = bool(bias or taps or qk_norm == "head" or slope_power or keep_first or talk or gate or v_mix
+                             or (position is not None and ((v_dim and v_dim != head_dim) or rotation != "half")))
+        plain = not (v_dim and v_dim != head_dim) and qk_norm == "none" and not chunk and not self.headwise
         if plain and head_dim % 16:
             raise ValueError(f"attention: head_dim {head_dim} is not a multiple of 16; the kernels refuse it")
         if head_dim > 512:
             raise ValueError(f"attention: head_dim {head_dim} is beyond the kernels' limit of 512")
-        if qk_norm not in ("none", "whole"):
-            raise ValueError(f"attention: unknown qk_norm '{qk_norm}' (none, whole)")
+        if qk_norm not in ("none", "whole", "head"):
+            raise ValueError(f"attention: unknown qk_norm '{qk_norm}' (none, whole, head)")
+        if v_mix not in (None, "source", "mixed"):
+            raise ValueError(f"attention: unknown v_mix '{v_mix}' (source, mixed)")
+        if taps < 0 or keep_first < 0 or slope_power < 0:
+            raise ValueError("attention: taps, keep_first and slope_power cannot be negative")
+        if keep_first and not window:
+            keep_first = 0                    # every key is visible anyway
+        if self.headwise and (qk_norm == "whole" or softcap):
+            raise ValueError("attention: a whole-row norm or a soft cap together with the head-wise options is not built")
+        if keep_first and chunk:
+            raise ValueError("attention: kept first keys together with a chunked mask are not built")
         self.hidden, self.n_q, self.n_kv, self.head_dim = hidden, n_q, n_kv, head_dim
         self.v_dim = int(v_dim) if v_dim else head_dim
         self.scale, self.softcap = float(scale), float(softcap or 0.0)
@@ -54,7 +97,13 @@ class Attention(Part):
         self.position = position
         self.q_dim, self.kv_dim, self.v_cols = n_q * head_dim, n_kv * head_dim, n_kv * self.v_dim
         # the options of the second paragraph above: their own row-wise kernel and the exact attention
-        self.rowwise = self.v_dim != head_dim or qk_norm != "none" or self.chunk is not None
+        self.bias, self.taps, self.slope_power, self.keep_first = bool(bias), int(taps), float(slope_power), int(keep_first)
+        self.talk, self.gate, self.v_mix, self.v_mix_key = bool(talk), bool(gate), v_mix, v_mix_key
+        self.cols = self.q_dim + self.kv_dim + self.v_cols
+        self.slopes = None
+        self.rowwise = (self.v_dim != head_dim or qk_norm != "none" or self.chunk is not None) and not self.headwise
+        if self.headwise and (self.v_dim > 512 or n_q > 128):
+            raise ValueError("attention: v_dim beyond 512 or more than 128 heads are beyond the head-wise kernels")
         if self.rowwise:
             if self.v_dim > 512:
                 raise ValueError(f"attention: v_dim {self.v_dim} is beyond the kernels' limit of 512")
@@ -67,14 +116,35 @@ class Attention(Part):
         if self.qk_norm == "whole":
             specs["q_norm"] = ParamSpec((self.q_dim,), "vector")
             specs["k_norm"] = ParamSpec((self.kv_dim,), "vector")
+        if self.bias:
+            specs.update(q_bias=ParamSpec((self.q_dim,), "vector"), k_bias=ParamSpec((self.kv_dim,), "vector"),
+                         v_bias=ParamSpec((self.v_cols,), "vector"), o_bias=ParamSpec((self.hidden,), "vector"))
+        if self.taps:
+            specs.update(q_conv=ParamSpec((self.q_dim, self.taps), "vector"), k_conv=ParamSpec((self.kv_dim, self.taps), "vector"),
+                         v_conv=ParamSpec((self.v_cols, self.taps), "vector"))
+        if self.talk:
+            specs["talk"] = ParamSpec((self.n_q, self.n_q), "vector")
+        if self.gate:
+            specs["gate"] = ParamSpec((self.n_q, self.hidden))
+        if self.v_mix:
+            specs["vmix"] = ParamSpec((), "vector")
         return specs
 
     def bind(self, params):
         # one projection for q, k and v: rows [Wq; Wk; Wv]
         kinds = {params[n].dtype for n in ("q", "k", "v")}
         dt = torch.float32 if (len(kinds) > 1 or torch.float32 in kinds) else next(iter(kinds))
-        self.w_qkv = torch.cat([params["q"].to(dt), params["k"].to(dt), params["v"].to(dt)], dim=0).contiguous()
+        rows = [params["q"].to(dt), params["k"].to(dt), params["v"].to(dt)]
+        if self.gate:
+            rows.append(params["gate"].to(dt))               # the gates' logits are columns of the same product
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
         self.w_o = params["o"]
+        f32 = lambda *names: torch.cat([params[n].float() for n in names], dim=0).contiguous()
+        self.in_bias = f32("q_bias", "k_bias", "v_bias") if self.bias else None
+        self.o_bias = params["o_bias"].float().contiguous() if self.bias else None
+        self.conv = f32("q_conv", "k_conv", "v_conv") if self.taps else None
+        self.w_talk = params["talk"].float().contiguous() if self.talk else None
+        self.lam = params["vmix"].float().reshape(1).contiguous() if self.v_mix == "mixed" else None
         self.q_gain = self.k_gain = None
         if self.qk_norm == "whole":
             gd = torch.float32 if params["q_norm"].dtype != params["k_norm"].dtype else params["q_norm"].dtype
@@ -82,6 +152,13 @@ class Attention(Part):
         self.params = {}
 
     def cache_spec(self):
+        if self.headwise:
+            kv = KVSpec(self.n_kv, self.head_dim, self.window, v_dim=self.v_dim if self.v_dim != self.head_dim else None,
+                        chunk=self.chunk, keep_first=self.keep_first)
+            if not self.taps:
+                return kv
+            # the convolution's last taps - 1 inputs (the projected q | k | v of those tokens, biases included)
+            return (kv, StateSpec((max(1, (self.taps - 1) * self.cols),), torch.float32))
         if self.rowwise:
             return KVSpec(self.n_kv, self.head_dim, self.window, v_dim=self.v_dim if self.v_dim != self.head_dim else None,
                           chunk=self.chunk)
@@ -90,10 +167,16 @@ class Attention(Part):
     def prepare(self, max_positions, device):
         if self.position is not None:
             self.position.prepare(max_positions, device)
+        if self.slope_power and (self.slopes is None or self.slopes.device != torch.device(device)):
+            h = torch.arange(1, self.n_q + 1, dtype=torch.float64)
+            self.slopes = torch.pow(torch.tensor(2.0, dtype=torch.float64), -self.slope_power * h / self.n_q) \
+                .to(torch.float32).to(device)
 
     def forward(self, x: torch.Tensor, ctx, entry, writes_cache: bool = True) -> torch.Tensor:
         """x (tokens, hidden) in the step's element type -> (tokens, hidden) float32, or
         [parts, tokens, hidden] partial sums that the residual kernel adds."""
+        if self.headwise:
+            return self._forward_headwise(x, ctx, entry, writes_cache)
         k_pages, v_pages, table, ring, page = ctx.kv(entry)
         if self.rowwise:
             return self._forward_rowwise(x, ctx, entry, writes_cache)
@@ -166,6 +249,75 @@ class Attention(Part):
             kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k_pages=k_pages, v_pages=v_pages, page_table=table,
                                    ring=ring, page_size=page, **common)
         return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
+
+    def _forward_headwise(self, x, ctx, entry, writes_cache):
+        """The path of a layer with one of the head-wise options of the module's third paragraph."""
+        if not writes_cache:
+            raise NotImplementedError("a layer of this kind cannot run on another layer's cache")
+        kv_entry, conv_entry = (entry.parts[0], entry.parts[1]) if self.taps else (entry, None)
+        k_pages, v_pages, table, ring, page = ctx.kv(kv_entry)
+        T, cols, dev = x.shape[0], self.cols, x.device
+        proj = linear(x, self.w_qkv, out_dtype=torch.float32)             # [ q | k | v | gate logits ]
+        rows, bias = proj[:, :cols], self.in_bias
+        if self.taps:
+            seq = (ctx.cu_q, ctx.kv_len, ctx.slots_dev, ctx.state(conv_entry))
+            conv = torch.empty((T, cols), dtype=torch.float32, device=dev)
+            kernels.causal_conv(rows, bias, self.conv, None, "none", ctx.tok_seq, ctx.positions, *seq, 0, conv)
+            kernels.conv_tail(rows, bias, self.taps, *seq, 0, ctx.batch)
+            rows, bias = conv, None
+        mix = v_first = v_keep = None
+        if self.v_mix == "source":
+            v_keep = ctx.carry[self.v_mix_key] = torch.empty((T, self.v_cols), dtype=torch.float32, device=dev)
+        elif self.v_mix == "mixed":
+            if self.v_mix_key not in ctx.carry:
+                raise RuntimeError(f"attention: no earlier layer of this pass left '{self.v_mix_key}'")
+            mix, v_first = self.lam, ctx.carry[self.v_mix_key]
+        qkv = torch.empty((T, cols), dtype=ctx.dtype, device=dev)
+        pos = self.position
+        kernels.qkv_finish(rows, bias, self.n_q, self.n_kv, self.head_dim, self.v_dim, ctx.positions, qkv,
+                           head_norm=self.qk_norm == "head", eps=self.eps,
+                           cos_sin=pos.table if pos is not None else None,
+                           rotary_dim=pos.rotary_dim if pos is not None else 0,
+                           pairing=pos.pairing if pos is not None else "half", mix=mix, v_first=v_first, v_keep=v_keep,
+                           k_pages=k_pages, v_pages=v_pages, cache_rows=ctx.cache_rows[kv_entry.group_id], page_size=page)
+        q = qkv[:, :self.q_dim]
+        k, v = qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
+        group = self.n_q // self.n_kv
+        common = dict(n_kv=self.n_kv, group=group, head_dim=self.head_dim, scale=self.scale, cap=0.0,
+                      window=self.window or 0, batch=ctx.batch, max_q_len=ctx.max_q_len)
+        out = torch.empty((T, self.n_q * self.v_dim), dtype=ctx.dtype, device=dev)
+        special = self.talk or self.gate or self.slopes is not None or self.keep_first or self.chunk
+        if not special and self.v_dim == self.head_dim and self.head_dim % 16 == 0 and self._tensor_cores(ctx):
+            # nothing the tensor-core kernels do not know: the same attention as a plain layer's
+            if ctx.mode == "prefill":
+                self.attend_packed(q, k, v, out, ctx, common)
+            else:
+                self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
+        else:
+            exact = dict(common, v_dim=self.v_dim, chunk=self.chunk or 0, slopes=self.slopes, keep_first=self.keep_first)
+            if ctx.mode == "prefill":
+                source = dict(k=k, v=v)
+            else:
+                source = dict(k_pages=k_pages, v_pages=v_pages, page_table=table, ring=ring, page_size=page,
+                              ring_from=ctx.ring_from(kv_entry))
+            if self.talk:
+                # every head's weights on the values of every kv head, then the mixing (and the gate) row by row
+                acc = torch.empty((T, self.n_q * self.n_kv * self.v_dim), dtype=torch.float32, device=dev)
+                kernels.attention_all_values(q, acc, ctx.cu_q, ctx.kv_len, **exact, **source)
+                kernels.heads_mix(acc, self.w_talk, proj[:, cols:] if self.gate else None, out, self.n_q, self.n_kv,
+                                  self.v_dim)
+            elif self.gate:
+                acc = torch.empty((T, self.n_q * self.v_dim), dtype=torch.float32, device=dev)
+                kernels.attention_simt(q, acc, ctx.cu_q, ctx.kv_len, **exact, **source)
+                kernels.heads_mix(acc, None, proj[:, cols:], out, self.n_q, self.n_kv, self.v_dim)
+            else:
+                kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, **exact, **source)
+        y = linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
+        if self.o_bias is None:
+            return y
+        biased = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+        kernels.bias_act(y, self.o_bias, "none", biased)
+        return biased
 
     # bfloat16 runs on the tensor cores when the sizes allow; everything else, and
     # all of float32, takes the exact CUDA-core kernel

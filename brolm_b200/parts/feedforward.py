@@ -11,15 +11,20 @@ from .linear import linear
 class GatedFeedForward(Part):
     """down(act(gate(x)) * up(x)), dense, no bias
     (wlejon/brolm src/gemma2.cpp:378-382 with act = gelu, tanh form).
-    Gate and up run as one product over the rows [Wg; Wu]."""
+    Gate and up run as one product over the rows [Wg; Wu].
+
+    ``activation`` "clamped_gate" is a pair function of its own instead of act(gate) * up:
+    g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1), with ``limit`` > 0."""
 
     kind = "feedforward"
     graph_safe = True
 
-    def __init__(self, hidden: int, inter: int, activation: str = "gelu_tanh"):
+    def __init__(self, hidden: int, inter: int, activation: str = "gelu_tanh", limit: float = 0.0):
         if activation not in kernels.ACTIVATIONS:
             raise ValueError(f"feed-forward: unknown activation '{activation}'")
-        self.hidden, self.inter, self.activation = hidden, inter, activation
+        if activation == "clamped_gate" and not limit > 0:
+            raise ValueError("feed-forward: the clamped gate needs a positive limit")
+        self.hidden, self.inter, self.activation, self.limit = hidden, inter, activation, float(limit)
 
     def param_specs(self):
         return {"gate": ParamSpec((self.inter, self.hidden)), "up": ParamSpec((self.inter, self.hidden)),
@@ -37,16 +42,16 @@ class GatedFeedForward(Part):
         act = torch.empty((x.shape[0], self.inter), dtype=ctx.dtype, device=x.device)
         if kernels.skinny_ok(x, self.w_gate_up):
             # few tokens: both products and the activation in one pass over the weights
-            kernels.skinny_gemm(x, self.w_gate_up, act, "gated", self.activation)
+            kernels.skinny_gemm(x, self.w_gate_up, act, "gated", self.activation, limit=self.limit)
         elif self.inter % 64 == 0 and kernels.stream_rows(x, self.w_gate_up):
             # 17 to 128 tokens: the same on the tcgen05 weight stream
-            kernels.gemm_stream(x, self.w_gate_up, act, "gated", self.activation)
+            kernels.gemm_stream(x, self.w_gate_up, act, "gated", self.activation, limit=self.limit)
         elif self.inter % 128 == 0 and kernels.gemm_tc_ok(x, self.w_gate_up, gated=True):
             # many tokens: the activation is the epilogue of the product; [gate | up] never reaches memory
-            kernels.gemm_tc(x, self.w_gate_up, act, "gated", self.activation)
+            kernels.gemm_tc(x, self.w_gate_up, act, "gated", self.activation, limit=self.limit)
         else:
             gate_up = linear(x, self.w_gate_up, out_dtype=ctx.dtype)
-            kernels.gated_act(gate_up, act, self.activation)
+            kernels.gated_act(gate_up, act, self.activation, self.limit)
         return linear(act, self.w_down, out_dtype=torch.float32, parts_ok=True)
 
 

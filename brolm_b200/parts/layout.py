@@ -60,6 +60,8 @@ class ModelLayout:
     weight_std: float = 0.02          # random-weights mode: matrices and tables
     norm_std: float = 0.1             # random-weights mode: vectors
     stream_parts: dict = dataclasses.field(default_factory=dict)   # name -> PartSpec of kind "stream"
+    # checkpoint name -> shape of tensors that a checkpoint may carry although nothing reads them
+    unused_tensors: dict = dataclasses.field(default_factory=dict)
 
     def __post_init__(self):
         for i, call in enumerate(self.schedule):

@@ -9,7 +9,9 @@ from .base import Part, register_part
 
 
 class RotaryEmbedding(Part):
-    """Rotation of the pairs (i, i + rot/2) of a head by pos * theta^(-2i/rot).
+    """Rotation of the pairs (i, i + rot/2) of a head by pos * theta^(-2i/rot); with ``pairing``
+    "interleaved" the pair of that angle is (2i, 2i + 1) instead (the table is the same, the kernel that
+    rotates is told which elements belong together).
 
     Frequencies as wlejon/brolm states them (src/qwen35_text.cpp:220-256);
     the pairing is the checkpoint's, see csrc/core.cu.  The table of
@@ -19,7 +21,10 @@ class RotaryEmbedding(Part):
 
     kind = "position"
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None, pairing: str = "half"):
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotary: unknown pairing '{pairing}' (half, interleaved)")
+        self.pairing = pairing
         self.head_dim = head_dim
         self.theta = float(theta)
         self.rotary_dim = rotary_dim or head_dim

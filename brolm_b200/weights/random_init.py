@@ -80,7 +80,7 @@ def random_tensor(seed: int, name: str, shape, std: float, dtype: torch.dtype, d
     for start in range(0, n, CHUNK):
         count = min(CHUNK, n - start)
         out[start:start + count] = normal_values(key, start, count, std, device).to(dtype)
-    return out.view(*shape)
+    return out.view(tuple(int(s) for s in shape))
 
 
 def random_tensors(expected: dict[str, Expected], seed: int, weight_std: float, norm_std: float,
