@@ -111,7 +111,7 @@ def write_safetensors(path: str, tensors: Iterable[tuple[str, torch.Tensor]] | d
             if t.dtype not in _NAMES:
                 raise SafetensorsError(f"safetensors: dtype {t.dtype} of '{name}' cannot be stored")
             t = t.detach().to("cpu").contiguous()
-            raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+            raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
             header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                             "data_offsets": [offset, offset + len(raw)]}
             out.write(raw)
