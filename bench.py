@@ -436,6 +436,120 @@ def neburax_main(args, pk) -> int:
     return 0
 
 
+# --arch kedasun: rotary layers (values mixed across layers) alternating with windowed layers that keep a sequence's
+# first keys (short convolutions, unit-norm heads, distance slopes, mixed heads' weights, a gate per head), each with a
+# dense clamped feed-forward between grouped norms
+KEDASUN_SIZES = {
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot=64, window=1024, keep_first=4, conv=4, ff=8192,
+              groups=4, vocab=32768),
+    "m": dict(width=3072, heads=24, kv_heads=8, dim=128, vdim=64, rot=64, window=2048, keep_first=8, conv=3, ff=12288,
+              groups=8, vocab=65536),
+}
+
+
+def kedasun_main(args, pk) -> int:
+    import torch
+
+    import brolm_b200 as bb
+
+    name = args.size if args.size in KEDASUN_SIZES else "s"
+    z = KEDASUN_SIZES[name]
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    W, H, G, d, dv, ff, win = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ff"], z["window"]
+    mlp = dict(kind="dense", ff=ff, limit=7.0)
+    rotary = dict(type="attention", mlp=mlp,
+                  mixer=dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, rot=dict(base=10000.0, dims=z["rot"]),
+                             v_mix=True))
+    windowed = dict(type="attention_2", mlp=mlp,
+                    mixer=dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, conv=z["conv"],
+                               mask=dict(size=win, keep_first=z["keep_first"]), v_mix=True))
+    layers = [rotary, windowed, rotary, windowed]
+    kcfg = bb.KedasunConfig.from_dict(dict(architecture="Kedasun", vocab=z["vocab"], width=W, layers=layers,
+                                           embedding=dict(scale=1.0), norm=dict(eps=1e-5, groups=z["groups"])))
+    runs = len(layers)
+    gcfg = bb.Gemma2Config(vocab_size=z["vocab"], hidden_size=W, intermediate_size=ff, num_hidden_layers=runs,
+                           num_attention_heads=H, num_key_value_heads=G, head_dim=d, query_pre_attn_scalar=float(d),
+                           sliding_window=win, layer_types=("full_attention", "sliding_attention") * (runs // 2),
+                           max_position_embeddings=8192)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps, warmup, batch = args.steps or 64, max(args.warmup, 3), args.batch or 8
+    context, prompt_len = args.context or 2304, 2048
+    common = (dev, flush, steps, warmup, batch, context, prompt_len)
+    b, gm = measure_design(kcfg, z["vocab"], *common), measure_design(gcfg, z["vocab"], *common)
+    T = prompt_len
+    full = T * (T + 1) // 2                                                   # visible (query, key) pairs, every key
+    wkeys = win * (win + 1) // 2 + (T - win) * win if T > win else full       # ... under a window
+    kept = sum(min(z["keep_first"], max(0, p + 1 - win)) for p in range(T))   # ... and the kept first keys beyond it
+    tf, gb = pk["bf16_burst"] * 1e12, pk["hbm_gbs"] * 1e9
+    n_rot, n_win = 2, 2
+    cols = H * d + G * d + G * dv
+    dec_full = batch * context * G * (d + dv) * 2.0
+    dec_win = batch * min(context, win + z["keep_first"]) * G * (d + dv) * 2.0
+    # (kernel-name fragment, work of all its launches in one pass over the layers, bound)
+    rows = [
+        ("kedasun prefill", b["prefill_kernels"], [
+            ("gemm_tc2_kernel<1>", runs * 2.0 * T * W * 2 * ff, "flops"),
+            ("attn_prefill", n_rot * 2.0 * H * (d + dv) * full, "flops"),
+            ("attn_headmix_prefill", n_win * 2.0 * H * (d + dv) * (wkeys + kept), "flops"),
+            ("attn_simt", n_rot * 2.0 * H * (d + dv) * full, "flops"),
+            ("attn_all_values", n_win * 2.0 * H * (d + G * dv) * (wkeys + kept), "flops"),
+            ("qkv_finish", runs * T * cols * (4.0 + 2.0 + 2.0), "bytes"),
+            ("causal_conv", n_win * T * cols * 8.0, "bytes"),
+            ("group_norm", 4 * runs * T * W * 8.0, "bytes"),
+        ]),
+        ("closest prefill", gm["prefill_kernels"], [
+            ("gemm_tc2_kernel<1>", runs * 2.0 * T * W * 2 * ff, "flops"),
+            ("attn_prefill_tc", n_rot * 4.0 * H * d * full + n_win * 4.0 * H * d * wkeys, "flops"),
+            ("rope_kv_write", runs * T * (H * d + 2 * G * d) * (2.0 + 2.0 + 2.0), "bytes"),
+            ("rmsnorm", 4 * runs * T * W * 8.0, "bytes"),
+        ]),
+        ("kedasun decode", b["decode_kernels"], [
+            ("skinny_kernel<2, 1, 1>", runs * 2 * ff * W * 2.0, "bytes"),
+            ("attn_decode", n_rot * dec_full, "bytes"),
+            ("attn_headmix_decode", n_win * dec_win, "bytes"),
+            ("attn_simt", n_rot * dec_full, "bytes"),
+            ("attn_all_values", n_win * dec_win, "bytes"),
+        ]),
+        ("closest decode", gm["decode_kernels"], [
+            ("skinny_kernel<2, 1, 1>", runs * 2 * ff * W * 2.0, "bytes"),
+            ("attn_decode_mma", (n_rot * batch * context + n_win * batch * min(context, win)) * 2 * G * d * 2.0, "bytes"),
+        ]),
+    ]
+    table = []
+    for title, kern, wanted in rows:
+        for frag, work, bound in wanted:
+            us = sum(v["us"] for k, v in kern.items() if frag in k)
+            n = sum(v["n"] for k, v in kern.items() if frag in k)
+            if not n:
+                continue
+            frac = work / (us * 1e-6) / (tf if bound == "flops" else gb)
+            table.append({"step": title, "kernel": frag, "launches": n, "us": round(us, 2),
+                          "bound": "tensor" if bound == "flops" else "hbm", "frac_of_measured_peak": round(frac, 4)})
+    result = {
+        "metric": f"Kedasun decode tokens/s (size {name}, batch {batch}, context {context}) beside Gemma 2 at equal sizes",
+        "value": round(batch * 1000.0 / b["decode_ms"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(b["decode_ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "brolm_b200", "clocks": b["clocks"], "gpu_launches": b["launches"],
+        "config": {"model": "Kedasun", **{k: v for k, v in z.items()}, "layer_runs": runs, "global_batch": batch,
+                   "seq_len": context, "prompt": prompt_len,
+                   "closest": {"model": "Gemma 2", "hidden": W, "heads": H, "kv_heads": G, "head_dim": d,
+                               "intermediate": ff, "layers": runs, "sliding_window": win},
+                   "l2": "the prompt is timed after an L2 flush; a decode step reads more than the L2 holds",
+                   "peaks": pk["source"]},
+        "kedasun": {"prefill_tok_s": round(T * 1000.0 / b["prefill_ms"], 1), "prefill_ms": round(b["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / b["decode_ms"], 1), "decode_ms": round(b["decode_ms"], 4)},
+        "closest": {"prefill_tok_s": round(T * 1000.0 / gm["prefill_ms"], 1), "prefill_ms": round(gm["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / gm["decode_ms"], 1), "decode_ms": round(gm["decode_ms"], 4)},
+        "kernels": table,
+        "by_kernel_us": {"kedasun_prefill": _top(b["prefill_kernels"], 24), "closest_prefill": _top(gm["prefill_kernels"]),
+                         "kedasun_decode": _top(b["decode_kernels"], 24), "closest_decode": _top(gm["decode_kernels"])},
+    }
+    print(json.dumps(result))
+    return 0
+
+
 def _by_kernel(events) -> dict:
     """Device records -> {kernel name: {"us": total time, "n": launches}}."""
     out: dict = {}
@@ -454,8 +568,8 @@ def _top(kern: dict, n: int = 14) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik", "neburax"],
-                    help="banevik, neburax: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m)")
+    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik", "neburax", "kedasun"],
+                    help="banevik, neburax, kedasun: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=0, help="decode steps in a timed region (default 64; 128 for 9b)")
     ap.add_argument("--warmup", type=int, default=8)
@@ -481,8 +595,10 @@ def main() -> int:
         return banevik_main(args, peaks())
     if args.arch == "neburax":
         return neburax_main(args, peaks())
+    if args.arch == "kedasun":
+        return kedasun_main(args, peaks())
     if args.size not in SIZES:
-        print(f"bench.py: --size {args.size} goes with --arch banevik or neburax")
+        print(f"bench.py: --size {args.size} goes with --arch banevik, neburax or kedasun")
         return 2
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
