@@ -1172,6 +1172,78 @@ def attention_all_values(q: torch.Tensor, acc: torch.Tensor, cu_q: torch.Tensor,
                        **args)
 
 
+def attention_headmix_ok(head_dim: int, v_dim: int, group: int, decode: bool, page_size: int = 64) -> bool:
+    """Whether the tensor-core kernels with the head-wise options take these sizes (bfloat16 only)."""
+    ok = head_dim % 16 == 0 and v_dim % 16 == 0 and 0 < head_dim <= 256 and 0 < v_dim <= 256
+    return ok and (not decode or (group <= 16 and page_size == 64))
+
+
+def headmix_splits(batch: int, blocks_y: int, max_kv_len: int, window: int, keep_first: int,
+                   sms: Optional[int] = None) -> int:
+    """How many blocks share the visible keys of one (sequence, block row) when decoding: one round of blocks
+    over the SMs, at least two tiles a block, at most 40."""
+    sms = sms or device_sms()
+    keys = min(max_kv_len, window + 63 + (keep_first + 63) // 64 * 64) if window > 0 else max_kv_len
+    tiles = max(1, (keys + 63) // 64)
+    return max(1, min(sms // max(1, batch * blocks_y), (tiles + 1) // 2, 40))
+
+
+def attention_headmix_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
+                              n_kv: int, group: int, head_dim: int, v_dim: int, scale: float, window: int, batch: int,
+                              max_q_len: int, slopes: Optional[torch.Tensor] = None, keep_first: int = 0,
+                              all_values: bool = False) -> None:
+    """Tensor-core attention (bfloat16 operands) of whole prompts that start at position 0, with value rows of
+    their own size, distance slopes and a window that keeps first keys.  ``out`` is bfloat16 or float32,
+    (tokens, heads * v_dim); with ``all_values`` every head's weights meet the values of every kv head and
+    ``out`` is (tokens, heads * n_kv * v_dim), head h's row being [n_kv][v_dim]."""
+    _check_sink(slopes, n_kv * group)
+    assert q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert out.shape[-1] >= n_kv * group * v_dim * (n_kv if all_values else 1) and cu_q.dtype == torch.int32
+    f = _fn("attn_headmix", "brolm_attn_headmix_prefill",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(cu_q),
+             _ptr(k), k.stride(0), _ptr(v), v.stride(0), n_kv, group, head_dim, v_dim, scale, int(window),
+             int(keep_first), _ptr(slopes), 1 if all_values else 0, batch, max_q_len, _stream()),
+           "attention_headmix_prefill")
+
+
+def attention_headmix_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                             k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor, *, ring: int,
+                             ring_from: int, page_size: int, n_kv: int, group: int, head_dim: int, v_dim: int,
+                             scale: float, window: int, batch: int, n_splits: int,
+                             slopes: Optional[torch.Tensor] = None, keep_first: int = 0,
+                             all_values: bool = False) -> None:
+    """The same attention for one new token per sequence over the paged cache (pages of 64 keys, at most 16
+    query heads per kv head).  The splits' partial results go through float32 scratch made here; the block
+    that finishes last among them merges them."""
+    _check_sink(slopes, n_kv * group)
+    assert q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16
+    assert out.dtype in (torch.bfloat16, torch.float32) and q.stride(-1) == 1 and out.stride(-1) == 1
+    assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim) and tuple(v_pages.shape[1:]) == (n_kv, page_size, v_dim)
+    assert page_table.dtype == torch.int32 and page_table.stride(1) == 1
+    assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
+    n_vh = n_kv if all_values else 1
+    assert out.shape[-1] >= n_kv * group * v_dim * n_vh
+    part_o = part_ml = None
+    if n_splits > 1:
+        n = batch * n_kv * group * n_vh * n_splits
+        both = torch.empty(n * (v_dim + 2), dtype=torch.float32, device=q.device)
+        part_o, part_ml = both[:n * v_dim], both[n * v_dim:]
+    f = _fn("attn_headmix", "brolm_attn_headmix_decode",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(cu_q),
+             _ptr(kv_len), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.stride(0), ring, int(ring_from),
+             page_size, n_kv, group, head_dim, v_dim, scale, int(window), int(keep_first), _ptr(slopes),
+             1 if all_values else 0, batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()),
+           "attention_headmix_decode")
+
+
 def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:
     if sink is not None:
         assert sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_q

@@ -47,6 +47,7 @@ LIBRARIES: dict[str, list[str]] = {
     "rowwise": ["rowwise.cu"],
     "recurrent": ["recurrent.cu"],
     "headwise": ["headwise.cu"],
+    "attn_headmix": ["attn_headmix.cu"],
     "groupnorm": ["groupnorm.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]

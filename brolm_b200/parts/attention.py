@@ -37,7 +37,9 @@ head h reads kv head h // (H / G)):
   meet the values, w'_h = sum_g talk[h, g] w_g, head h applying w'_h to the
   values of its own kv head.  The attention kernel applies every head's
   weights to the values of every kv head (float results [H, G, v_dim]) and a
-  row-wise kernel takes the sums over g;
+  row-wise kernel takes the sums over g;  in bfloat16 that kernel, like the
+  one for slopes, kept first keys and value rows of their own size, runs on
+  the tensor cores (``attention_headmix_*``);
 * ``gate``: head h's result is multiplied by sigmoid(W_g x)_h, W_g being H rows
   of the fused projection;
 * ``v_mix``: "source" leaves the layer's values of the step's tokens (float,
@@ -300,18 +302,41 @@ class Attention(Part):
             else:
                 source = dict(k_pages=k_pages, v_pages=v_pages, page_table=table, ring=ring, page_size=page,
                               ring_from=ctx.ring_from(kv_entry))
+            # bfloat16 without a chunked mask runs on the tensor cores, all else on the exact kernel
+            tensor = self._tensor_cores(ctx) and not self.chunk and \
+                kernels.attention_headmix_ok(self.head_dim, self.v_dim, group, ctx.mode != "prefill", page)
+
+            def attend(dst, all_values=False):
+                if not tensor:
+                    if all_values:
+                        kernels.attention_all_values(q, dst, ctx.cu_q, ctx.kv_len, **exact, **source)
+                    else:
+                        kernels.attention_simt(q, dst, ctx.cu_q, ctx.kv_len, **exact, **source)
+                    return
+                args = dict(n_kv=self.n_kv, group=group, head_dim=self.head_dim, v_dim=self.v_dim, scale=self.scale,
+                            window=self.window or 0, batch=ctx.batch, slopes=self.slopes, keep_first=self.keep_first,
+                            all_values=all_values)
+                if ctx.mode == "prefill":
+                    kernels.attention_headmix_prefill(q, dst, ctx.cu_q, k, v, max_q_len=ctx.max_q_len, **args)
+                else:
+                    splits = kernels.headmix_splits(ctx.batch, self.n_kv * (self.n_kv if all_values else 1),
+                                                    ctx.max_kv_len, self.window or 0, self.keep_first)
+                    kernels.attention_headmix_decode(q, dst, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring,
+                                                     ring_from=ctx.ring_from(kv_entry), page_size=page,
+                                                     n_splits=splits, **args)
+
             if self.talk:
                 # every head's weights on the values of every kv head, then the mixing (and the gate) row by row
                 acc = torch.empty((T, self.n_q * self.n_kv * self.v_dim), dtype=torch.float32, device=dev)
-                kernels.attention_all_values(q, acc, ctx.cu_q, ctx.kv_len, **exact, **source)
+                attend(acc, all_values=True)
                 kernels.heads_mix(acc, self.w_talk, proj[:, cols:] if self.gate else None, out, self.n_q, self.n_kv,
                                   self.v_dim)
             elif self.gate:
                 acc = torch.empty((T, self.n_q * self.v_dim), dtype=torch.float32, device=dev)
-                kernels.attention_simt(q, acc, ctx.cu_q, ctx.kv_len, **exact, **source)
+                attend(acc)
                 kernels.heads_mix(acc, None, proj[:, cols:], out, self.n_q, self.n_kv, self.v_dim)
             else:
-                kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, **exact, **source)
+                attend(out)
         y = linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
         if self.o_bias is None:
             return y

@@ -62,7 +62,18 @@ CFG_U = dict(
             windowed(2, 1, 16, 8, 0.3, 2, size=1, keep_first=2, v_mix=False, mlp=dense(24, 0.9)),
             rotary(4, 1, 16, 16, 0.25, 16, v_mix=False, mlp=dense(48, 1.1))])
 
-CONFIGS = {"S": (CFG_S, 3, 0.15), "T": (CFG_T, 4, 0.2), "U": (CFG_U, 5, 0.2)}      # name -> (config, seed, weight std)
+# V: head sizes that are multiples of 16, keys and values of different sizes: in bfloat16 every layer's attention runs on
+# the tensor cores; windows across a page's border that keep keys within and beyond the first page, several key/value
+# heads under mixed weights, a rotary layer with value rows of their own size.
+CFG_V = dict(
+    architecture="Kedasun", vocab=80, width=64, embedding=dict(scale=1.5), norm=dict(eps=1e-5, groups=2),
+    layers=[windowed(4, 2, 32, 48, 0.3, 3, size=70, keep_first=5, mlp=dense(48, 1.5)),
+            rotary(4, 2, 16, 48, 0.3, 8, mlp=dense(40, 2.0)),
+            windowed(6, 3, 16, 32, 0.35, 2, size=64, keep_first=66, mlp=dense(32, 1.0)),
+            windowed(2, 1, 48, 16, 0.25, 4, size=130, keep_first=1, v_mix=False),
+            rotary(2, 2, 32, 48, 0.25, 32, base=300.0, mlp=dense(40, 1.5))])
+
+CONFIGS = {"S": (CFG_S, 3, 0.15), "T": (CFG_T, 4, 0.2), "U": (CFG_U, 5, 0.2), "V": (CFG_V, 6, 0.15)}      # name -> (config, seed, weight std)
 
 
 def shape_up(tensors: dict, seed: int) -> dict:

@@ -23,7 +23,8 @@ ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)),
 # Largest error of a logit against the float64 oracle, relative to the largest logit of the compared rows.
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}
 STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
-CASES = [("S", "float32"), ("S", "bfloat16"), ("T", "float32"), ("T", "bfloat16"), ("U", "float32"), ("U", "bfloat16")]
+CASES = [("S", "float32"), ("S", "bfloat16"), ("T", "float32"), ("T", "bfloat16"), ("U", "float32"), ("U", "bfloat16"),
+         ("V", "float32"), ("V", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
@@ -134,7 +135,7 @@ def test_unequal_batches_against_each_alone(setups, name, dtype):
     assert eng.cache.live_slots == 0 and all(g.pool.held_pages == 0 for g in eng.cache.kv_groups)
 
 
-@pytest.mark.parametrize("name,dtype", [("S", "float32"), ("S", "bfloat16"), ("T", "float32"), ("U", "float32")])
+@pytest.mark.parametrize("name,dtype", [("S", "float32"), ("S", "bfloat16"), ("T", "float32"), ("U", "float32"), ("V", "bfloat16")])
 def test_long_decoding_from_the_first_tokens(setups, name, dtype):
     _, config, weights, model = setups[(name, dtype)]
     (p,) = random_prompts(config["vocab"], [300], seed=14)
