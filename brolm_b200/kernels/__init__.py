@@ -1178,14 +1178,19 @@ def attention_headmix_ok(head_dim: int, v_dim: int, group: int, decode: bool, pa
     return ok and (not decode or (group <= 16 and page_size == 64))
 
 
+HEADMIX_ROUNDS = int(os.environ.get("BROLM_HEADMIX_ROUNDS", "2"))
+
+
 def headmix_splits(batch: int, blocks_y: int, max_kv_len: int, window: int, keep_first: int,
                    sms: Optional[int] = None) -> int:
-    """How many blocks share the visible keys of one (sequence, block row) when decoding: one round of blocks
-    over the SMs, at least two tiles a block, at most 40."""
+    """How many blocks share the visible keys of one (sequence, block row) when decoding: ``HEADMIX_ROUNDS``
+    blocks per SM over the whole grid (a block walks its tiles one after another and two are resident on an
+    SM, so with many block rows short walks beat one round of long ones), at least two tiles a block, at
+    most 40."""
     sms = sms or device_sms()
     keys = min(max_kv_len, window + 63 + (keep_first + 63) // 64 * 64) if window > 0 else max_kv_len
     tiles = max(1, (keys + 63) // 64)
-    return max(1, min(sms // max(1, batch * blocks_y), (tiles + 1) // 2, 40))
+    return max(1, min(HEADMIX_ROUNDS * sms // max(1, batch * blocks_y), (tiles + 1) // 2, 40))
 
 
 def attention_headmix_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
