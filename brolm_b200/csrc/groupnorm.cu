@@ -9,7 +9,8 @@
 //     residual_group_rmsnorm:  h += post ? gnorm(y; w_post) : y;   out = next ? gnorm(h; w_next) : h   (out optional)
 //
 // h is the float residual stream; y may come as partial sums [parts][rows][hidden] that are added in order.
-// One block of 256 threads per row.  A row is cut into segments (a group, or an equal piece of a group when
+// One block of 256 threads per row; a lane takes four elements at a time when the sizes and addresses allow.
+// A row is cut into segments (a group, or an equal piece of a group when
 // there are fewer groups than warps); a warp takes whole segments, sums their squares in lane order and leaves
 // one partial sum per segment, and a group's statistic is the sum of its segments' partial sums in order: the
 // order of every addition is fixed by the sizes alone, never by what else runs.  The row stays in shared
@@ -46,7 +47,43 @@ __device__ __forceinline__ float group_inv(const float* partial, const Segments&
     return rsqrtf(t / (float)s.gs + eps);
 }
 
-template <typename X, typename W, typename O>
+
+// V elements at once (V = 1, or 4 when every segment, the row and all addresses allow 16-byte steps)
+template <int V> __device__ __forceinline__ void ld(const float* p, float (&v)[V]) {
+    if constexpr (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+        v[0] = *p;
+    }
+}
+template <int V> __device__ __forceinline__ void ld(const bf16* p, float (&v)[V]) {
+    if constexpr (V == 4) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else {
+        v[0] = __bfloat162float(*p);
+    }
+}
+template <int V> __device__ __forceinline__ void st(float* p, const float (&v)[V]) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else *p = v[0];
+}
+template <int V> __device__ __forceinline__ void st(bf16* p, const float (&v)[V]) {
+    if constexpr (V == 4) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&a);
+        u.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    } else {
+        *p = __float2bfloat16_rn(v[0]);
+    }
+}
+
+template <typename X, typename W, typename O, int V>
 __global__ void __launch_bounds__(THREADS) group_rmsnorm_kernel(const X* __restrict__ x, const int32_t* __restrict__ rows,
                                                                 const W* __restrict__ w, float eps, float offset,
                                                                 O* __restrict__ out, int hidden, int groups) {
@@ -63,10 +100,12 @@ __global__ void __launch_bounds__(THREADS) group_rmsnorm_kernel(const X* __restr
         const int g = sg / s.sub, k = sg - g * s.sub;
         const int lo = g * s.gs + k * s.seg, hi = min(g * s.gs + s.gs, lo + s.seg);
         float ss = 0.0f;
-        for (int i = lo + lane; i < hi; i += 32) {
-            const float v = to_float(xr[i]);
-            row[i] = v;
-            ss += v * v;
+        for (int i = lo + lane * V; i < hi; i += 32 * V) {
+            float v[V];
+            ld<V>(xr + i, v);
+            st<V>(row + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss += v[e] * v[e];
         }
         ss = warp_sum(ss);
         if (lane == 0) partial[sg] = ss;
@@ -77,11 +116,18 @@ __global__ void __launch_bounds__(THREADS) group_rmsnorm_kernel(const X* __restr
         const int g = sg / s.sub, k = sg - g * s.sub;
         const int lo = g * s.gs + k * s.seg, hi = min(g * s.gs + s.gs, lo + s.seg);
         const float inv = group_inv(partial, s, g, eps);
-        for (int i = lo + lane; i < hi; i += 32) orow[i] = from_float<O>(row[i] * inv * (offset + to_float(w[i])));
+        for (int i = lo + lane * V; i < hi; i += 32 * V) {
+            float v[V], g_[V];
+            ld<V>(row + i, v);
+            ld<V>(w + i, g_);
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] = v[e] * inv * (offset + g_[e]);
+            st<V>(orow + i, v);
+        }
     }
 }
 
-template <typename Y, typename W, typename O>
+template <typename Y, typename W, typename O, int V>
 __global__ void __launch_bounds__(THREADS) residual_group_rmsnorm_kernel(
     float* __restrict__ h, const Y* __restrict__ y, int n_parts, long long part_stride, const W* __restrict__ w_post,
     float eps_post, float off_post, const W* __restrict__ w_next, float eps_next, float off_next, O* __restrict__ out,
@@ -99,11 +145,18 @@ __global__ void __launch_bounds__(THREADS) residual_group_rmsnorm_kernel(
         const int g = sg / s.sub, k = sg - g * s.sub;
         const int lo = g * s.gs + k * s.seg, hi = min(g * s.gs + s.gs, lo + s.seg);
         float ss = 0.0f;
-        for (int i = lo + lane; i < hi; i += 32) {
-            float v = to_float(y[base + i]);
-            for (int p = 1; p < n_parts; ++p) v += to_float(y[(size_t)p * part_stride + base + i]);
-            row[i] = v;
-            ss += v * v;
+        for (int i = lo + lane * V; i < hi; i += 32 * V) {
+            float v[V];
+            ld<V>(y + base + i, v);
+            for (int p = 1; p < n_parts; ++p) {
+                float t[V];
+                ld<V>(y + (size_t)p * part_stride + base + i, t);
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[e] += t[e];
+            }
+            st<V>(row + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss += v[e] * v[e];
         }
         ss = warp_sum(ss);
         if (lane == 0) partial[sg] = ss;
@@ -115,13 +168,23 @@ __global__ void __launch_bounds__(THREADS) residual_group_rmsnorm_kernel(
         const int lo = g * s.gs + k * s.seg, hi = min(g * s.gs + s.gs, lo + s.seg);
         const float inv = w_post ? group_inv(partial, s, g, eps_post) : 1.0f;
         float ss = 0.0f;
-        for (int i = lo + lane; i < hi; i += 32) {
-            float v = row[i];
-            if (w_post) v = v * inv * (off_post + to_float(w_post[i]));
-            const float hn = h[base + i] + v;
-            h[base + i] = hn;
-            row[i] = hn;
-            ss += hn * hn;
+        for (int i = lo + lane * V; i < hi; i += 32 * V) {
+            float v[V], hn[V];
+            ld<V>(row + i, v);
+            if (w_post) {
+                float g_[V];
+                ld<V>(w_post + i, g_);
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[e] = v[e] * inv * (off_post + g_[e]);
+            }
+            ld<V>(h + base + i, hn);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                hn[e] += v[e];
+                ss += hn[e] * hn[e];
+            }
+            st<V>(h + base + i, hn);
+            st<V>(row + i, hn);
         }
         ss = warp_sum(ss);
         if (lane == 0) partial[s.n + sg] = ss;
@@ -132,10 +195,16 @@ __global__ void __launch_bounds__(THREADS) residual_group_rmsnorm_kernel(
         const int g = sg / s.sub, k = sg - g * s.sub;
         const int lo = g * s.gs + k * s.seg, hi = min(g * s.gs + s.gs, lo + s.seg);
         const float inv = w_next ? group_inv(partial + s.n, s, g, eps_next) : 1.0f;
-        for (int i = lo + lane; i < hi; i += 32) {
-            float v = row[i];
-            if (w_next) v = v * inv * (off_next + to_float(w_next[i]));
-            out[base + i] = from_float<O>(v);
+        for (int i = lo + lane * V; i < hi; i += 32 * V) {
+            float v[V];
+            ld<V>(row + i, v);
+            if (w_next) {
+                float g_[V];
+                ld<V>(w_next + i, g_);
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[e] = v[e] * inv * (off_next + g_[e]);
+            }
+            st<V>(out + base + i, v);
         }
     }
 }
@@ -159,24 +228,42 @@ int allow_smem(K kernel, size_t smem, size_t* allowed) {
     return BROLM_OK;
 }
 
+// whether every segment begins and ends at a multiple of four elements
+inline bool by_four(int hidden, int groups) {
+    const Segments s = make_segments(hidden, groups);
+    return hidden % 4 == 0 && s.gs % 4 == 0 && s.seg % 4 == 0;
+}
+template <typename... P> bool aligned16(P... p) { return (((uintptr_t)p | ...) & 15) == 0; }
+
 template <typename X, typename W, typename O>
 int launch_norm(const void* x, const void* rows, const void* w, float eps, float offset, void* out, int n, int hidden,
                 int groups, size_t smem, cudaStream_t stream) {
-    static size_t allowed = 0;
-    if (int e = allow_smem(group_rmsnorm_kernel<X, W, O>, smem, &allowed)) return e;
-    return launch_pdl(group_rmsnorm_kernel<X, W, O>, dim3(n), dim3(THREADS), smem, stream, (const X*)x, (const int32_t*)rows,
-                      (const W*)w, eps, offset, (O*)out, hidden, groups);
+    static size_t allowed[2] = {0, 0};
+    if (by_four(hidden, groups) && aligned16(x, w, out)) {
+        if (int e = allow_smem(group_rmsnorm_kernel<X, W, O, 4>, smem, &allowed[1])) return e;
+        return launch_pdl(group_rmsnorm_kernel<X, W, O, 4>, dim3(n), dim3(THREADS), smem, stream, (const X*)x,
+                          (const int32_t*)rows, (const W*)w, eps, offset, (O*)out, hidden, groups);
+    }
+    if (int e = allow_smem(group_rmsnorm_kernel<X, W, O, 1>, smem, &allowed[0])) return e;
+    return launch_pdl(group_rmsnorm_kernel<X, W, O, 1>, dim3(n), dim3(THREADS), smem, stream, (const X*)x,
+                      (const int32_t*)rows, (const W*)w, eps, offset, (O*)out, hidden, groups);
 }
 
 template <typename Y, typename W, typename O>
 int launch_residual(void* h, const void* y, int n_parts, long long part_stride, const void* w_post, float eps_post,
                     float off_post, const void* w_next, float eps_next, float off_next, void* out, int n, int hidden,
                     int groups, size_t smem, cudaStream_t stream) {
-    static size_t allowed = 0;
-    if (int e = allow_smem(residual_group_rmsnorm_kernel<Y, W, O>, smem, &allowed)) return e;
-    return launch_pdl(residual_group_rmsnorm_kernel<Y, W, O>, dim3(n), dim3(THREADS), smem, stream, (float*)h, (const Y*)y,
-                      n_parts, part_stride, (const W*)w_post, eps_post, off_post, (const W*)w_next, eps_next, off_next,
-                      (O*)out, hidden, groups);
+    static size_t allowed[2] = {0, 0};
+    if (by_four(hidden, groups) && part_stride % 4 == 0 && aligned16(h, y, w_post, w_next, out)) {
+        if (int e = allow_smem(residual_group_rmsnorm_kernel<Y, W, O, 4>, smem, &allowed[1])) return e;
+        return launch_pdl(residual_group_rmsnorm_kernel<Y, W, O, 4>, dim3(n), dim3(THREADS), smem, stream, (float*)h,
+                          (const Y*)y, n_parts, part_stride, (const W*)w_post, eps_post, off_post, (const W*)w_next,
+                          eps_next, off_next, (O*)out, hidden, groups);
+    }
+    if (int e = allow_smem(residual_group_rmsnorm_kernel<Y, W, O, 1>, smem, &allowed[0])) return e;
+    return launch_pdl(residual_group_rmsnorm_kernel<Y, W, O, 1>, dim3(n), dim3(THREADS), smem, stream, (float*)h,
+                      (const Y*)y, n_parts, part_stride, (const W*)w_post, eps_post, off_post, (const W*)w_next, eps_next,
+                      off_next, (O*)out, hidden, groups);
 }
 
 }  // namespace
