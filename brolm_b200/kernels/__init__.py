@@ -1181,16 +1181,33 @@ def attention_headmix_ok(head_dim: int, v_dim: int, group: int, decode: bool, pa
 HEADMIX_ROUNDS = int(os.environ.get("BROLM_HEADMIX_ROUNDS", "2"))
 
 
+def attention_headmix_shares_keys(head_dim: int, v_dim: int, n_kv: int, group: int, all_values: bool) -> bool:
+    """Whether a decode step of these sizes runs the kernel that keeps the value rows of every kv head in one
+    block (at most 8 query heads per kv head, n_kv * v_dim up to 512, a stage of keys and values twice in shared
+    memory): its grid has n_kv block rows a sequence, the other kernel's n_kv * n_kv.  The launcher's own rule."""
+    key = (head_dim, v_dim, n_kv, group, bool(all_values))
+    got = _shares_memo.get(key)
+    if got is None:
+        f = _fn("attn_headmix", "brolm_attn_headmix_decode_shares_keys", [c_int, c_int, c_int, c_int, c_int, c_int])
+        got = _shares_memo[key] = bool(f(head_dim, v_dim, n_kv, group, 1 if all_values else 0, 40))
+    return got
+
+
+_shares_memo: dict = {}
+
+
 def headmix_splits(batch: int, blocks_y: int, max_kv_len: int, window: int, keep_first: int,
-                   sms: Optional[int] = None) -> int:
-    """How many blocks share the visible keys of one (sequence, block row) when decoding: ``HEADMIX_ROUNDS``
-    blocks per SM over the whole grid (a block walks its tiles one after another and two are resident on an
-    SM, so with many block rows short walks beat one round of long ones), at least two tiles a block, at
-    most 40."""
+                   sms: Optional[int] = None, rounds: Optional[int] = None) -> int:
+    """How many blocks share the visible keys of one (sequence, block row) when decoding: ``rounds`` blocks per
+    SM over the whole grid (default ``HEADMIX_ROUNDS``: a block walks its tiles one after another and two are
+    resident on an SM, so with many block rows short walks beat one round of long ones; the kernel that keeps
+    every value head in a block holds an SM alone and takes one round), at least two tiles a block, at most 40."""
     sms = sms or device_sms()
     keys = min(max_kv_len, window + 63 + (keep_first + 63) // 64 * 64) if window > 0 else max_kv_len
     tiles = max(1, (keys + 63) // 64)
-    return max(1, min(HEADMIX_ROUNDS * sms // max(1, batch * blocks_y), (tiles + 1) // 2, 40))
+    if batch * blocks_y > 65536:
+        return 1                       # more block rows than the splits' tickets
+    return max(1, min((rounds or HEADMIX_ROUNDS) * sms // max(1, batch * blocks_y), (tiles + 1) // 2, 40))
 
 
 def attention_headmix_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,

@@ -319,8 +319,10 @@ class Attention(Part):
                 if ctx.mode == "prefill":
                     kernels.attention_headmix_prefill(q, dst, ctx.cu_q, k, v, max_q_len=ctx.max_q_len, **args)
                 else:
-                    splits = kernels.headmix_splits(ctx.batch, self.n_kv * (self.n_kv if all_values else 1),
-                                                    ctx.max_kv_len, self.window or 0, self.keep_first)
+                    shares = kernels.attention_headmix_shares_keys(self.head_dim, self.v_dim, self.n_kv, group, all_values)
+                    rows = self.n_kv * (self.n_kv if all_values and not shares else 1)
+                    splits = kernels.headmix_splits(ctx.batch, rows, ctx.max_kv_len, self.window or 0, self.keep_first,
+                                                    rounds=1 if shares else None)
                     kernels.attention_headmix_decode(q, dst, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring,
                                                      ring_from=ctx.ring_from(kv_entry), page_size=page,
                                                      n_splits=splits, **args)

@@ -47,6 +47,9 @@ CASES = [  # H, G, hd, vd, window, keep, slopes, all_values
     (8, 2, 128, 128, 100, 1, True, True),
     (4, 4, 16, 32, 1, 2, True, False),
     (16, 1, 80, 144, 200, 65, False, True),
+    (20, 2, 16, 32, 90, 2, True, True),         # ten heads a kv head: too many for the decode kernel that shares keys
+    (8, 4, 64, 128, 150, 7, True, True),        # 32 tiles of 16 value elements: that kernel's largest form
+    (8, 8, 32, 128, 70, 3, True, True),         # 64 such tiles: beyond it
 ]
 
 
