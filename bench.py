@@ -500,7 +500,7 @@ def kedasun_main(args, pk) -> int:
         ]),
         ("closest prefill", gm["prefill_kernels"], [
             ("gemm_tc2_kernel<1>", runs * 2.0 * T * W * 2 * ff, "flops"),
-            ("attn_prefill_tc", n_rot * 4.0 * H * d * full + n_win * 4.0 * H * d * wkeys, "flops"),
+            ("attn_prefill", n_rot * 4.0 * H * d * full + n_win * 4.0 * H * d * wkeys, "flops"),
             ("rope_kv_write", runs * T * (H * d + 2 * G * d) * (2.0 + 2.0 + 2.0), "bytes"),
             ("rmsnorm", 4 * runs * T * W * 8.0, "bytes"),
         ]),
