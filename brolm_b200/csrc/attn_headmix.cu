@@ -13,6 +13,9 @@
 //
 // Scores, the mask, the softmax statistics and the output accumulator are float; the weights are rounded to
 // bfloat16 for the second product.  The output is float (what the mixing reads) or bfloat16.
+// Decoding has a second kernel for `n_vh` > 1, up to 8 query heads a kv head and n_kv * vd up to 512: one block per
+// (split, kv head of the keys, sequence) keeps the value rows of every kv head beside the keys, computes the scores
+// once and runs the second product transposed (see there).
 // The tile machinery (64 keys a tile, four warps, cp.async staging, XOR-swizzled rows of whole 128-byte lines)
 // is that of attn_mma.cuh.
 #include "attn_mma.cuh"
@@ -389,7 +392,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_decode_kernel(HmArgs a)
     const int q_row = a.cu_q[b];
     __syncthreads();
     pdl_wait();               // q and the newest key and value come from the kernels before this one
-    const int n_q = a.n_kv * a.group;
     const int pos = kv_len - 1;
     const int window = a.window > 0 ? a.window : 0x3fffffff;
     const int keep = a.window > 0 ? a.keep_first : 0;
