@@ -51,6 +51,11 @@ struct FinishArgs {
     int page_size;
 };
 
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 template <typename X, typename O>
 __global__ void __launch_bounds__(256) qkv_finish_kernel(FinishArgs a) {
     extern __shared__ __align__(16) float row[];      // the token's q | k | v as floats
@@ -63,13 +68,39 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(FinishArgs a) {
     pdl_wait();
     if (pos < 0) return;                               // a padding row
     const X* pr = (const X*)a.proj + (size_t)t * a.ldp;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        float v = to_float(pr[i]);
-        for (int p = 1; p < a.n_parts; ++p) v += to_float(pr[(size_t)p * a.part_stride + i]);
-        if (a.bias) v += a.bias[i];
-        row[i] = v;
+    bool by_four = false;
+    if constexpr (sizeof(X) == 4) {
+        // float rows whose parts, bias and row all begin at multiples of 16 bytes: four numbers a load
+        by_four = (cols & 3) == 0 && (a.ldp & 3) == 0 && (a.part_stride & 3) == 0 && ((uintptr_t)a.proj & 15) == 0 &&
+                  ((uintptr_t)a.bias & 15) == 0;
+        if (by_four) {
+            const float* pf = reinterpret_cast<const float*>(pr);
+            for (int i = threadIdx.x * 4; i < cols; i += blockDim.x * 4) {
+                float4 v = *reinterpret_cast<const float4*>(pf + i);
+                for (int p = 1; p < a.n_parts; ++p) {
+                    const float4 u = *reinterpret_cast<const float4*>(pf + (size_t)p * a.part_stride + i);
+                    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+                }
+                if (a.bias) {
+                    const float4 u = *reinterpret_cast<const float4*>(a.bias + i);
+                    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+                }
+                *reinterpret_cast<float4*>(row + i) = v;
+            }
+        }
+    }
+    if (!by_four) {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            float v = to_float(pr[i]);
+            for (int p = 1; p < a.n_parts; ++p) v += to_float(pr[(size_t)p * a.part_stride + i]);
+            if (a.bias) v += a.bias[i];
+            row[i] = v;
+        }
     }
     __syncthreads();
+    // two neighbours a lane and one store for both, when every row they go to begins at an even element
+    const bool pairs = (a.hd & 1) == 0 && (a.vd & 1) == 0 && (a.ldo & 1) == 0 && ((uintptr_t)a.out & 7) == 0 &&
+                       ((uintptr_t)a.k_pages & 7) == 0 && ((uintptr_t)a.v_pages & 7) == 0 && ((uintptr_t)a.v_keep & 7) == 0;
     const int crow = a.k_pages ? a.cache_rows[t] : -1;
     const size_t page = crow >= 0 ? (size_t)(crow / a.page_size) : 0, place = crow >= 0 ? (size_t)(crow % a.page_size) : 0;
     O* orow = (O*)a.out + (size_t)t * a.ldo;
@@ -87,8 +118,7 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(FinishArgs a) {
         }
         const bool is_k = head >= a.n_q;
         O* kdst = (is_k && crow >= 0) ? (O*)a.k_pages + ((page * a.n_kv + (head - a.n_q)) * a.page_size + place) * hd : nullptr;
-        for (int e = lane; e < hd; e += 32) {
-            float v;
+        auto value = [&](int e) -> float {
             if (cs && e < a.rot) {
                 int i, first;
                 float u, w;
@@ -106,19 +136,44 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(FinishArgs a) {
                 u *= inv;
                 w *= inv;
                 const float c = cs[2 * i], s = cs[2 * i + 1];
-                v = first ? u * c - w * s : w * c + u * s;
-            } else {
-                v = x[e] * inv;
+                return first ? u * c - w * s : w * c + u * s;
             }
-            const O o = from_float<O>(v);
-            orow[(size_t)head * hd + e] = o;
-            if (kdst) kdst[e] = o;
+            return x[e] * inv;
+        };
+        if (pairs) {
+            for (int e = 2 * lane; e < hd; e += 64) {
+                const float v0 = value(e), v1 = value(e + 1);
+                store_pair(orow + (size_t)head * hd + e, v0, v1);
+                if (kdst) store_pair(kdst + e, v0, v1);
+            }
+        } else {
+            for (int e = lane; e < hd; e += 32) {
+                const O o = from_float<O>(value(e));
+                orow[(size_t)head * hd + e] = o;
+                if (kdst) kdst[e] = o;
+            }
         }
     }
     // values
     const float lam = (a.lambda && a.v_first) ? *a.lambda : 0.0f;
     const float* vf = a.v_first ? a.v_first + (size_t)t * a.ld_first : nullptr;
     const int vd = a.vd;
+    if (pairs) {
+        for (int i = threadIdx.x * 2; i < v_cols; i += blockDim.x * 2) {
+            float v0 = row[q_cols + k_cols + i], v1 = row[q_cols + k_cols + i + 1];
+            if (a.v_keep) *reinterpret_cast<float2*>(a.v_keep + (size_t)t * v_cols + i) = make_float2(v0, v1);
+            if (vf) {
+                v0 = (1.0f - lam) * v0 + lam * vf[i];
+                v1 = (1.0f - lam) * v1 + lam * vf[i + 1];
+            }
+            store_pair(orow + q_cols + k_cols + i, v0, v1);
+            if (crow >= 0) {
+                const int g = i / vd, d = i - g * vd;
+                store_pair((O*)a.v_pages + ((page * a.n_kv + g) * a.page_size + place) * vd + d, v0, v1);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < v_cols; i += blockDim.x) {
         float v = row[q_cols + k_cols + i];
         if (a.v_keep) a.v_keep[(size_t)t * v_cols + i] = v;
