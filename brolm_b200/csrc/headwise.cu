@@ -200,6 +200,33 @@ __global__ void __launch_bounds__(256) heads_mix_kernel(const float* __restrict_
     const int t = blockIdx.x;
     const int group = heads / n_kv;
     const float* ar = acc + (size_t)t * ld_acc;
+    // four neighbours of a head's row a thread when rows and addresses allow 16-byte steps (with a few tokens there
+    // are threads to spare, and one number a thread is the shorter chain)
+    if (gridDim.x >= 64 && (vd & 3) == 0 && (ld_acc & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)acc & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < heads * vd; i += gridDim.y * blockDim.x * 4) {
+            const int h = i / vd, d = i - h * vd;
+            const int c = h / group;
+            float4 s4;
+            if (talk) {
+                s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int g = 0; g < heads; ++g) {
+                    const float w = tk[h * heads + g];
+                    const float4 v = *reinterpret_cast<const float4*>(ar + ((size_t)g * n_kv + c) * vd + d);
+                    s4.x = fmaf(w, v.x, s4.x); s4.y = fmaf(w, v.y, s4.y); s4.z = fmaf(w, v.z, s4.z); s4.w = fmaf(w, v.w, s4.w);
+                }
+            } else {
+                s4 = *reinterpret_cast<const float4*>(ar + i);
+            }
+            if (gate) {
+                const float gt = 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate + h]));
+                s4.x *= gt; s4.y *= gt; s4.z *= gt; s4.w *= gt;
+            }
+            O* dst = out + (size_t)t * ldo + i;
+            store_pair(dst, s4.x, s4.y);
+            store_pair(dst + 2, s4.z, s4.w);
+        }
+        return;
+    }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < heads * vd; i += gridDim.y * blockDim.x) {
         const int h = i / vd, d = i - h * vd;
         const int c = h / group;
