@@ -10,7 +10,7 @@ Public face, in the manner of wlejon/brolm's C++ API
     out    = brolm_b200.generate(engine, prompts, eos_id, GenerateOptions(...))
 """
 from . import models  # noqa: F401  (registers the architectures)
-from .config import BanevikConfig, ConfigError, Gemma2Config, KedasunConfig, ModelConfig, NeburaxConfig, load_config, register_architecture
+from .config import BanevikConfig, ConfigError, Gemma2Config, KedasunConfig, ModelConfig, NeburaxConfig, RitiraxConfig, load_config, register_architecture
 from .engine import DecoderModel, Engine, StepError, generate, load_model, write_random_model
 from .parts import register_part
 from .sampling import GenerateOptions, SamplingParams, Sampler
@@ -19,6 +19,6 @@ from .weights import WeightsError
 
 Model = DecoderModel
 
-__all__ = ["ConfigError", "Gemma2Config", "BanevikConfig", "NeburaxConfig", "KedasunConfig", "ModelConfig", "load_config", "register_architecture", "DecoderModel",
+__all__ = ["ConfigError", "Gemma2Config", "BanevikConfig", "NeburaxConfig", "KedasunConfig", "RitiraxConfig", "ModelConfig", "load_config", "register_architecture", "DecoderModel",
            "Model", "Engine", "StepError", "load_model", "write_random_model", "register_part", "WeightsError", "generate", "GenerateOptions", "SamplingParams",
            "Sampler", "GemmaTokenizer"]

@@ -4,6 +4,7 @@ from .banevik import BanevikConfig
 from .gemma2 import Gemma2Config
 from .kedasun import KedasunConfig
 from .neburax import NeburaxConfig
+from .ritirax import RitiraxConfig
 
-__all__ = ["Architecture", "ConfigError", "ModelConfig", "Gemma2Config", "BanevikConfig", "NeburaxConfig", "KedasunConfig", "architecture_of",
+__all__ = ["Architecture", "ConfigError", "ModelConfig", "Gemma2Config", "BanevikConfig", "NeburaxConfig", "KedasunConfig", "RitiraxConfig", "architecture_of",
            "load_config", "register_architecture", "registered_architectures"]

@@ -32,7 +32,10 @@
 // at once; the output row of a head is [n_kv][vd] and a call fills its kv heads' part of it (a caller
 // whose n_kv * vd is beyond the kernel's row limit calls several times); what a mixing of the heads'
 // weights after the softmax needs.  A float
-// output whatever the element type of q, k and v (`out_f32`).
+// output whatever the element type of q, k and v (`out_f32`).  A learned bias by distance: a table
+// [query heads][dist_len] of floats, of which key j adds entry min(p - j, dist_len - 1) of the head's row to its
+// score after the scale and the cap (the caller lays the table out by distance, whatever rule maps a distance
+// to a learned number).
 #include "common.cuh"
 
 namespace {
@@ -72,6 +75,8 @@ struct AttnArgs {
     int v_from;
     int vd_head;              // a kv head's value size
     int out_f32;              // the output is float whatever T is
+    const float* dist_bias;   // [n_kv * group][dist_len] or null: added to the capped score by min(p - j, dist_len - 1)
+    int dist_len;
 };
 
 // Place of position p in a sequence's pages: the first `from` places are held for good, the ring lies behind them.
@@ -138,10 +143,12 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
     // per-row state of this warp
     int rpos[RPW];
     float m[RPW], l[RPW], acc[RPW][DPL], slope[RPW];
+    const float* dbias[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         const int r = warp * RPW + i;
         rpos[i] = r < rows_here ? first_pos + (row0 + r) / a.group : -1;
+        dbias[i] = (a.dist_bias && r < rows_here) ? a.dist_bias + (size_t)(g * a.group + (row0 + r) % a.group) * a.dist_len : nullptr;
         slope[i] = (a.slopes && r < rows_here) ? a.slopes[g * a.group + (row0 + r) % a.group] : 0.0f;
         m[i] = -INFINITY;
         l[i] = 0.0f;
@@ -250,6 +257,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
                                  (a.chunk <= 0 || kp >= rpos[i] - rpos[i] % a.chunk);
             float sc = visible ? soft_cap(s[i] * a.scale, a.cap) : -INFINITY;
             if (visible && a.slopes) sc -= slope[i] * (float)(rpos[i] - kp);
+            if (visible && dbias[i]) sc += dbias[i][min(rpos[i] - kp, a.dist_len - 1)];
             const float tile_max = warp_max(sc);
             const float m_new = fmaxf(m[i], tile_max);
             float corr = 1.0f;
@@ -349,7 +357,8 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
                               const void* v_pages, const void* page_table, int pt_stride, int ring, int page_size,
                               int n_kv, int group, int hd, float scale, float cap, int window, const void* sink,
                               int batch, int max_q_len, int vd, int v_stride, int chunk, const void* slopes,
-                              int keep_first, int ring_from, int v_all, int v_from, int out_f32, cudaStream_t stream) {
+                              int keep_first, int ring_from, int v_all, int v_from, int out_f32, const void* dist_bias,
+                              int dist_len, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     if (hd <= 0 || hd > 512 || group <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
     const int vd_head = vd;
@@ -357,6 +366,7 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
     if (v_all) vd = vd * v_all;                        // a head's output row holds the values of several kv heads
     if (vd <= 0 || vd > 512) return BROLM_ERR_BAD_SIZE;
     if (keep_first < 0 || ring_from < 0 || (keep_first > 0 && chunk > 0)) return BROLM_ERR_BAD_SIZE;
+    if (dist_bias && dist_len <= 0) return BROLM_ERR_BAD_SIZE;
     bool vec = hd % 8 == 0 && vd_head % 8 == 0 && q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0;
     if (batch > 65535 || n_kv > 65535) return BROLM_ERR_TOO_LARGE;
     const bool paged = k_pages != nullptr;
@@ -376,6 +386,7 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.sink = (const float*)sink;
     a.slopes = (const float*)slopes; a.keep_first = window > 0 ? keep_first : 0; a.ring_from = ring_from; a.v_all = v_all; a.v_from = v_from;
     a.vd_head = vd_head; a.out_f32 = out_f32 ? 1 : 0;
+    a.dist_bias = (const float*)dist_bias; a.dist_len = dist_len;
     if (dtype == BROLM_F32) return dispatch<float>(a, paged, batch, max_q_len, stream);
     if (dtype == BROLM_BF16) return dispatch<bf16>(a, paged, batch, max_q_len, stream);
     return BROLM_ERR_BAD_DTYPE;

@@ -30,10 +30,20 @@ constexpr int GBM = 64, GBN = 64;
 // mode ROUTE_LOGISTIC: the weight of a chosen expert is the logistic function of its score.
 // mode ROUTE_SOFTMAX: s = softmax(z) over all experts; the choice goes by s + corr (a learned number per expert
 // that takes no part in the weights); the weights are the chosen s over their sum (+ 1e-20).
+// The softmax mode's further options (RouteOpts): the experts form `groups` equal groups of neighbours, a group's
+// score is the largest s + corr in it, and only experts of the `keep` best groups (ties: the lower group) can be
+// chosen; `renorm` 0 leaves the chosen s as they are instead of dividing by their sum; `wscale` multiplies the
+// weights at the end.
 enum : int { ROUTE_LOGISTIC = 0, ROUTE_SOFTMAX = 1 };
 
+struct RouteOpts {
+    int groups, keep, renorm;
+    float wscale;
+};
+
 __device__ __forceinline__ void pick_top(float* zr, int E, int top, int t, int lane, int32_t* __restrict__ ids,
-                                         float* __restrict__ wts, int mode, const float* __restrict__ corr) {
+                                         float* __restrict__ wts, int mode, const float* __restrict__ corr,
+                                         RouteOpts ro) {
     if (mode == ROUTE_SOFTMAX) {
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
@@ -48,6 +58,32 @@ __device__ __forceinline__ void pick_top(float* zr, int E, int top, int t, int l
         const float inv = 1.0f / sum;
         for (int e = lane; e < E; e += 32) zr[e] *= inv;
         __syncwarp();
+        if (ro.groups > 1 && ro.keep < ro.groups) {
+            // groups - keep times: the group with the smallest score (ties: the higher group) leaves; a group that
+            // has left holds -inf in every place, which no score of a group still in is
+            const int size = E / ro.groups;
+            for (int out = 0; out < ro.groups - ro.keep; ++out) {
+                float worst = INFINITY;
+                int at = -1;
+                for (int g = lane; g < ro.groups; g += 32) {
+                    float best = -INFINITY;
+                    for (int j = 0; j < size; ++j) {
+                        const int e = g * size + j;
+                        if (zr[e] > -INFINITY) best = fmaxf(best, zr[e] + (corr ? corr[e] : 0.0f));
+                    }
+                    if (best > -INFINITY && (best < worst || (best == worst && g > at))) { worst = best; at = g; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ow = __shfl_xor_sync(0xffffffffu, worst, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (oa >= 0 && (at < 0 || ow < worst || (ow == worst && oa > at))) { worst = ow; at = oa; }
+                }
+                if (at < 0) break;
+                for (int j = lane; j < size; j += 32) zr[at * size + j] = -INFINITY;
+                __syncwarp();
+            }
+        }
         float total = 0.0f;
         for (int k = 0; k < top; ++k) {
             float best = -INFINITY;
@@ -74,7 +110,7 @@ __device__ __forceinline__ void pick_top(float* zr, int E, int top, int t, int l
             __syncwarp();
         }
         if (lane == 0) {
-            const float inv_total = 1.0f / (total + 1e-20f);
+            const float inv_total = (ro.renorm ? 1.0f / (total + 1e-20f) : 1.0f) * ro.wscale;
             for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= inv_total;
         }
         return;
@@ -106,7 +142,7 @@ template <typename T, int RT>
 __global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ wr,
                                                     int E, int D, int top, int tokens, int vec,
                                                     int32_t* __restrict__ ids, float* __restrict__ wts, int mode,
-                                                    const float* __restrict__ corr) {
+                                                    const float* __restrict__ corr, RouteOpts ro) {
     extern __shared__ float z[];                       // [RT][E]
     const int t0 = blockIdx.x * RT;
     const int nt = min(RT, tokens - t0);
@@ -181,14 +217,14 @@ __global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __
         }
     }
     __syncthreads();
-    for (int r = warp; r < nt; r += nwarps) pick_top(z + r * E, E, top, t0 + r, lane, ids, wts, mode, corr);
+    for (int r = warp; r < nt; r += nwarps) pick_top(z + r * E, E, top, t0 + r, lane, ids, wts, mode, corr, ro);
 }
 
 // The choice alone, for scores that a matrix product left in memory: z [tokens, E] float (ldz between rows).
 // A block takes eight tokens, a warp one.
 __global__ void __launch_bounds__(256) route_pick_kernel(const float* __restrict__ zs, long ldz, int E, int top, int tokens,
                                                          int32_t* __restrict__ ids, float* __restrict__ wts, int mode,
-                                                         const float* __restrict__ corr) {
+                                                         const float* __restrict__ corr, RouteOpts ro) {
     extern __shared__ float z[];                       // [8][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 8 + warp;
@@ -196,7 +232,7 @@ __global__ void __launch_bounds__(256) route_pick_kernel(const float* __restrict
     float* zr = z + warp * E;
     for (int e = lane; e < E; e += 32) zr[e] = zs[(size_t)t * ldz + e];
     __syncwarp();
-    pick_top(zr, E, top, t, lane, ids, wts, mode, corr);
+    pick_top(zr, E, top, t, lane, ids, wts, mode, corr, ro);
 }
 
 // ---------------------------------------------------------------------------
@@ -667,10 +703,18 @@ int launch_grouped(int dtype, GroupedArgs& g, int row_tiles, bool few, cudaStrea
 // ids [tokens, top] int32 and wts [tokens, top] float: the chosen experts of every token, best first.
 // mode 0: the weights are the logistic function of the chosen scores; mode 1: softmax over all experts, the choice
 // by softmax + corr (float [experts] or null), the weights the chosen softmax values over their sum.
+// groups, keep, renorm, wscale: the softmax mode's options (see RouteOpts); 1, 1, 1, 1.0 are the plain router.
+static inline bool route_opts_ok(int experts, int top, int groups, int keep) {
+    return groups >= 1 && keep >= 1 && keep <= groups && experts % groups == 0 && top <= keep * (experts / groups);
+}
+
 BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* wr, int tokens, int experts, int width,
-                               int top, void* ids, void* wts, int mode, const void* corr, cudaStream_t stream) {
+                               int top, void* ids, void* wts, int mode, const void* corr, int groups, int keep,
+                               int renorm, float wscale, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (experts <= 0 || top <= 0 || top > experts || width <= 0) return BROLM_ERR_BAD_SIZE;
+    if (!route_opts_ok(experts, top, groups, keep)) return BROLM_ERR_BAD_SIZE;
+    const RouteOpts ro = {groups, keep, renorm, wscale};
     if (experts > 8192) return BROLM_ERR_TOO_LARGE;
     const int vec = width % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)wr & 15) == 0;
     const bool many = tokens > 64 && experts <= 1024;      // (four rows of scores in the default shared memory)
@@ -679,7 +723,7 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
     const int blocks = (tokens + rt - 1) / rt;
 #define BROLM_ROUTE(T, RT)                                                                                        \
     route_kernel<T, RT><<<blocks, RT == 1 ? 1024 : 256, smem, stream>>>((const T*)x, ldx, (const T*)wr, experts, width, top, tokens, \
-                                                       vec, (int32_t*)ids, (float*)wts, mode, (const float*)corr)
+                                                       vec, (int32_t*)ids, (float*)wts, mode, (const float*)corr, ro)
     if (dtype == BROLM_F32) {
         if (many) BROLM_ROUTE(float, 4); else BROLM_ROUTE(float, 1);
     } else if (dtype == BROLM_BF16) {
@@ -693,12 +737,15 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
 
 // The same choice from scores already in memory: z [tokens, experts] float, ldz floats between rows.
 BROLM_API int brolm_route_pick(const void* z, long ldz, int tokens, int experts, int top, void* ids, void* wts,
-                               int mode, const void* corr, cudaStream_t stream) {
+                               int mode, const void* corr, int groups, int keep, int renorm, float wscale,
+                               cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (experts <= 0 || top <= 0 || top > experts) return BROLM_ERR_BAD_SIZE;
+    if (!route_opts_ok(experts, top, groups, keep)) return BROLM_ERR_BAD_SIZE;
+    const RouteOpts ro = {groups, keep, renorm, wscale};
     if (experts > 1024) return BROLM_ERR_TOO_LARGE;          // (eight rows of scores in the default shared memory)
     route_pick_kernel<<<(tokens + 7) / 8, 256, (size_t)8 * experts * sizeof(float), stream>>>(
-        (const float*)z, ldz, experts, top, tokens, (int32_t*)ids, (float*)wts, mode, (const float*)corr);
+        (const float*)z, ldz, experts, top, tokens, (int32_t*)ids, (float*)wts, mode, (const float*)corr, ro);
     return launch_status();
 }
 

@@ -4,7 +4,8 @@
 //   [ q: n_q * hd | k: n_kv * hd | v: n_kv * vd ]:
 //     * the projection may arrive as float partial sums of K slices, which are added in order, and a bias
 //       (one number per column) is added to the sum;
-//     * unit norm per head: every q and k head is divided by sqrt(mean(head^2) + eps), no gain;
+//     * unit norm per head: every q and k head is divided by sqrt(mean(head^2) + eps); with `q_gain` / `k_gain`
+//       (hd floats each, one row for all heads) the normed head is multiplied by it element by element;
 //     * rotation of the first `rot` elements of every q and k head by pos * f_i, the angles' cos and sin from a
 //       table [position][rot / 2][2]; the pair of f_i is (i, i + rot/2) ("half", pairing 0) or (2i, 2i + 1)
 //       ("interleaved", pairing 1); the rest of the head passes unchanged;
@@ -36,6 +37,8 @@ struct FinishArgs {
     int n_q, n_kv, hd, vd;
     int head_norm;
     float eps;
+    const float* q_gain;       // [hd] or null: a gain for every query head after its unit norm
+    const float* k_gain;       // [hd] or null: the same for the key heads
     const int32_t* positions;
     const float* cos_sin;      // [positions][rot / 2][2] or null
     int rot, pairing;
@@ -117,6 +120,7 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(FinishArgs a) {
             inv = rsqrtf(ss / (float)hd + a.eps);
         }
         const bool is_k = head >= a.n_q;
+        const float* gain = a.head_norm ? (is_k ? a.k_gain : a.q_gain) : nullptr;
         O* kdst = (is_k && crow >= 0) ? (O*)a.k_pages + ((page * a.n_kv + (head - a.n_q)) * a.page_size + place) * hd : nullptr;
         auto value = [&](int e) -> float {
             if (cs && e < a.rot) {
@@ -135,10 +139,14 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(FinishArgs a) {
                 }
                 u *= inv;
                 w *= inv;
+                if (gain) {
+                    u *= a.pairing == 1 ? gain[2 * i] : gain[i];
+                    w *= a.pairing == 1 ? gain[2 * i + 1] : gain[i + half];
+                }
                 const float c = cs[2 * i], s = cs[2 * i + 1];
                 return first ? u * c - w * s : w * c + u * s;
             }
-            return x[e] * inv;
+            return gain ? x[e] * inv * gain[e] : x[e] * inv;
         };
         if (pairs) {
             for (int e = 2 * lane; e < hd; e += 64) {
@@ -247,7 +255,8 @@ BROLM_API int brolm_qkv_finish(const void* proj, int x_dtype, int n_parts, long 
                                int n_q, int n_kv, int hd, int vd, int head_norm, float eps, const void* positions,
                                const void* cos_sin, int rot, int pairing, const void* lambda, const void* v_first,
                                long ld_first, void* v_keep, void* out, int out_dtype, long ldo, void* k_pages, void* v_pages,
-                               const void* cache_rows, int page_size, int tokens, cudaStream_t stream) {
+                               const void* cache_rows, int page_size, int tokens, const void* q_gain, const void* k_gain,
+                               cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (n_q <= 0 || n_kv <= 0 || hd <= 0 || vd <= 0 || n_parts < 1) return BROLM_ERR_BAD_SIZE;
     if (cos_sin && (rot <= 0 || rot % 2 || rot > hd || pairing < 0 || pairing > 1)) return BROLM_ERR_BAD_SIZE;
@@ -261,6 +270,7 @@ BROLM_API int brolm_qkv_finish(const void* proj, int x_dtype, int n_parts, long 
     a.lambda = (const float*)lambda; a.v_first = (const float*)v_first; a.ld_first = ld_first; a.v_keep = (float*)v_keep;
     a.out = out; a.ldo = ldo; a.k_pages = k_pages; a.v_pages = v_pages; a.cache_rows = (const int32_t*)cache_rows;
     a.page_size = page_size;
+    a.q_gain = (const float*)q_gain; a.k_gain = (const float*)k_gain;
 #define BROLM_QF(X, O)                                                                                             \
     do {                                                                                                           \
         static size_t allowed = 0;                                                                                 \

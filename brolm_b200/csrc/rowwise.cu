@@ -8,7 +8,9 @@
 //                   value rows may have a size of their own
 //   gate_group_norm out = rmsnorm per group of (y * silu(z)) * gain
 //   experts_combine out = sum over a token's choices of weight * (expert's result | the token's own
-//                   row for an identity expert) + the shared expert's result
+//                   row for an identity expert) + the shared expert's result, the latter times
+//                   sigmoid(w . x) when a gate row w is given
+//   norm_sigmoid_gate  out = (y / rms(y) * gain, or y itself without a gain) * sigmoid(z)
 //
 // Inputs are float or bfloat16, outputs as asked for.  One block per token (row); a row's result
 // depends on that row alone.
@@ -169,11 +171,22 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
                                                               const X* __restrict__ x, long ldx,
                                                               const float* __restrict__ shared, int shared_parts,
                                                               long long shared_stride, float* __restrict__ out, int tokens,
-                                                              int hidden) {
+                                                              int hidden, const X* __restrict__ shared_gate) {
+    __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    float sg = 1.0f;
+    if (shared_gate && shared_parts > 0) {
+        // one number per token: the logistic function of the gate row's product with the token's input, summed
+        // in float by a fixed tree (every block of the token computes the same)
+        float dot = 0.0f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            dot = fmaf(to_float(shared_gate[i]), to_float(x[(size_t)t * ldx + i]), dot);
+        dot = block_sum(dot, scratch);
+        sg = 1.0f / (1.0f + expf(-dot));
+    }
     if (c >= hidden) return;
     float acc = 0.0f;
     for (int k = 0; k < top; ++k) {
@@ -182,8 +195,38 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
         const float v = e < n_real ? y[((size_t)k * tokens + t) * hidden + c] : to_float(x[(size_t)t * ldx + c]);
         acc = fmaf(w, v, acc);
     }
-    for (int s = 0; s < shared_parts; ++s) acc += shared[(size_t)s * shared_stride + (size_t)t * hidden + c];
-    out[(size_t)t * hidden + c] = acc;
+    float sh = 0.0f;
+    for (int s = 0; s < shared_parts; ++s) sh += shared[(size_t)s * shared_stride + (size_t)t * hidden + c];
+    out[(size_t)t * hidden + c] = fmaf(sg, sh, acc);
+}
+
+// out[t, i] = n(y)[t, i] * sigmoid(z[t, i]);  n(y) = y * rsqrt(mean(y^2) + eps) * w with a gain w, y itself
+// without one.  One block per token.
+template <typename Y, typename Z, typename W, typename O>
+__global__ void __launch_bounds__(256) norm_sigmoid_gate_kernel(const Y* __restrict__ y, long ldy, const Z* __restrict__ z, long ldz,
+                                                                const W* __restrict__ w, float eps, int cols,
+                                                                O* __restrict__ out, long ldo) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const Y* yr = y + (size_t)t * ldy;
+    const Z* zr = z + (size_t)t * ldz;
+    float inv = 1.0f;
+    if (w) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = to_float(yr[i]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        inv = rsqrtf(ss / (float)cols + eps);
+    }
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        float v = to_float(yr[i]);
+        if (w) v = v * inv * to_float(w[i]);
+        out[(size_t)t * ldo + i] = from_float<O>(v / (1.0f + expf(-to_float(zr[i]))));
+    }
 }
 
 }  // namespace
@@ -268,17 +311,44 @@ BROLM_API int brolm_gate_group_norm(const void* y, long ldy, const void* z, int 
 
 BROLM_API int brolm_experts_combine(const void* y, const void* ids, const void* wts, int top, int n_real, const void* x,
                                     int x_dtype, long ldx, const void* shared, int shared_parts, long long shared_stride,
-                                    void* out, int tokens, int hidden, cudaStream_t stream) {
+                                    void* out, int tokens, int hidden, const void* shared_gate, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (!shared) shared_parts = 0;
     dim3 grid(tokens, (hidden + 255) / 256);
     if (x_dtype == BROLM_F32)
         return launch_pdl(experts_combine_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
                           (const float*)wts, top, n_real, (const float*)x, ldx, (const float*)shared, shared_parts,
-                          shared_stride, (float*)out, tokens, hidden);
+                          shared_stride, (float*)out, tokens, hidden, (const float*)shared_gate);
     if (x_dtype == BROLM_BF16)
         return launch_pdl(experts_combine_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
                           (const float*)wts, top, n_real, (const bf16*)x, ldx, (const float*)shared, shared_parts,
-                          shared_stride, (float*)out, tokens, hidden);
+                          shared_stride, (float*)out, tokens, hidden, (const bf16*)shared_gate);
+    return BROLM_ERR_BAD_DTYPE;
+}
+
+// y, z and the gain w (null: no norm) are float or bfloat16 each; the result is float or bfloat16.
+BROLM_API int brolm_norm_sigmoid_gate(const void* y, int y_dtype, long ldy, const void* z, int z_dtype, long ldz,
+                                      const void* w, int w_dtype, float eps, int cols, void* out, int out_dtype, long ldo,
+                                      int tokens, cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (cols <= 0) return BROLM_ERR_BAD_SIZE;
+    if (!w) w_dtype = BROLM_F32;
+#define BROLM_NG(Y, Z, W, O) return launch_pdl(norm_sigmoid_gate_kernel<Y, Z, W, O>, dim3(tokens), dim3(256), 0, stream,                                                (const Y*)y, ldy, (const Z*)z, ldz, (const W*)w, eps, cols, (O*)out, ldo)
+#define BROLM_NG2(Y, Z, W)                                    \
+    do {                                                      \
+        if (out_dtype == BROLM_F32) BROLM_NG(Y, Z, W, float); \
+        if (out_dtype == BROLM_BF16) BROLM_NG(Y, Z, W, bf16); \
+        return BROLM_ERR_BAD_DTYPE;                           \
+    } while (0)
+    if (y_dtype == BROLM_F32 && z_dtype == BROLM_F32 && w_dtype == BROLM_F32) BROLM_NG2(float, float, float);
+    if (y_dtype == BROLM_F32 && z_dtype == BROLM_F32 && w_dtype == BROLM_BF16) BROLM_NG2(float, float, bf16);
+    if (y_dtype == BROLM_F32 && z_dtype == BROLM_BF16 && w_dtype == BROLM_BF16) BROLM_NG2(float, bf16, bf16);
+    if (y_dtype == BROLM_BF16 && z_dtype == BROLM_BF16 && w_dtype == BROLM_BF16) BROLM_NG2(bf16, bf16, bf16);
+    if (y_dtype == BROLM_BF16 && z_dtype == BROLM_BF16 && w_dtype == BROLM_F32) BROLM_NG2(bf16, bf16, float);
+    if (y_dtype == BROLM_BF16 && z_dtype == BROLM_F32 && w_dtype == BROLM_F32) BROLM_NG2(bf16, float, float);
+    if (y_dtype == BROLM_BF16 && z_dtype == BROLM_F32 && w_dtype == BROLM_BF16) BROLM_NG2(bf16, float, bf16);
+    if (y_dtype == BROLM_F32 && z_dtype == BROLM_BF16 && w_dtype == BROLM_F32) BROLM_NG2(float, bf16, float);
+#undef BROLM_NG2
+#undef BROLM_NG
     return BROLM_ERR_BAD_DTYPE;
 }

@@ -264,7 +264,7 @@ def latent_rows(proj: torch.Tensor, q_cols: int, positions: torch.Tensor, cos_si
     part | zeros], the same row into ``pages`` at ``cache_rows`` (negative: not kept), and the rotated query
     parts into columns rank .. of every head of ``qlat`` (tokens, heads * Dp)."""
     Dp = lat.shape[1]
-    assert proj.stride(1) == 1 and proj.shape[1] == q_cols + rank + dr and q_cols == heads * (dn + dr)
+    assert proj.stride(1) == 1 and proj.shape[1] >= q_cols + rank + dr and q_cols == heads * (dn + dr)
     assert lat.dtype == proj.dtype and qlat.dtype == proj.dtype and gain.dtype == proj.dtype
     assert lat.is_contiguous() and qlat.is_contiguous() and qlat.shape == (proj.shape[0], heads * Dp)
     assert gain.is_contiguous() and gain.numel() == rank
@@ -293,33 +293,47 @@ def _check_route(mode: str, correction: Optional[torch.Tensor], experts: int) ->
         assert correction.numel() == experts
 
 
+def _route_opts(mode: str, experts: int, top: int, groups: int, keep: int, renorm: bool, scale: float) -> tuple:
+    if (groups, keep, renorm, scale) != (1, 1, True, 1.0) and mode != "softmax":
+        raise KernelError("router: groups, unnormalised weights and a scale go with the softmax mode")
+    if groups < 1 or not 1 <= keep <= groups or experts % groups or top > keep * (experts // groups):
+        raise KernelError(f"router: {experts} experts in {groups} groups of which {keep} stay open cannot give {top} choices")
+    return int(groups), int(keep), 1 if renorm else 0, float(scale)
+
+
 def route_topk(x: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor,
-               mode: str = "logistic", correction: Optional[torch.Tensor] = None) -> None:
+               mode: str = "logistic", correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1,
+               renorm: bool = True, scale: float = 1.0) -> None:
     """ids, weights [tokens, top]: the ``top`` experts with the largest score, best first (ties: the lower index).
     ``mode`` "logistic": the score is z = router.x (float32 sums) and the weight its logistic function.
     ``mode`` "softmax": s = softmax(z) over all experts, the choice goes by s + ``correction`` (float32 [experts],
-    no part of the weights) and the weights are the chosen s over their sum (+ 1e-20)."""
+    no part of the weights) and the weights are the chosen s over their sum (+ 1e-20).  In that mode the experts may
+    form ``groups`` equal groups of neighbours, of which only the ``keep`` with the largest best score stay open to
+    the choice; ``renorm`` False leaves the chosen s undivided; ``scale`` multiplies the weights."""
     assert x.dtype == router.dtype and x.stride(1) == 1 and router.is_contiguous() and router.shape[1] == x.shape[1]
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
     assert ids.shape == (x.shape[0], top) and weights.shape == ids.shape
     _check_route(mode, correction, router.shape[0])
+    opts = _route_opts(mode, router.shape[0], top, groups, keep, renorm, scale)
     f = _fn("grouped", "brolm_route_topk", [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                                            c_void_p, c_int, c_void_p, c_void_p])
+                                            c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_code(x), _ptr(x), x.stride(0), _ptr(router), x.shape[0], router.shape[0], x.shape[1], top, _ptr(ids),
-             _ptr(weights), ROUTE_MODES[mode], _ptr(correction), _stream()), "route_topk")
+             _ptr(weights), ROUTE_MODES[mode], _ptr(correction), *opts, _stream()), "route_topk")
 
 
 def route_pick(z: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, mode: str = "logistic",
-               correction: Optional[torch.Tensor] = None) -> None:
+               correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, renorm: bool = True,
+               scale: float = 1.0) -> None:
     """The choice of ``route_topk`` from scores z [tokens, experts] float32 that a matrix product left in memory."""
     assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1 and z.shape[1] <= 1024
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
     assert ids.shape == (z.shape[0], top) and weights.shape == ids.shape
     _check_route(mode, correction, z.shape[1])
+    opts = _route_opts(mode, z.shape[1], top, groups, keep, renorm, scale)
     f = _fn("grouped", "brolm_route_pick", [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
-                                            c_void_p])
+                                            c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(z), z.stride(0), z.shape[0], z.shape[1], top, _ptr(ids), _ptr(weights), ROUTE_MODES[mode],
-             _ptr(correction), _stream()), "route_pick")
+             _ptr(correction), *opts, _stream()), "route_pick")
 
 
 GROUP_ROWS = 64          # rows of a tile of the grouped product
@@ -527,10 +541,10 @@ def qkv_finish(proj: torch.Tensor, bias: Optional[torch.Tensor], n_q: int, n_kv:
                mix: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None,
                v_keep: Optional[torch.Tensor] = None, k_pages: Optional[torch.Tensor] = None,
                v_pages: Optional[torch.Tensor] = None, cache_rows: Optional[torch.Tensor] = None,
-               page_size: int = 64) -> None:
+               page_size: int = 64, q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None) -> None:
     """A projection's rows [q: n_q * head_dim | k: n_kv * head_dim | v: n_kv * v_dim] made ready for attention:
     ``proj`` (tokens, cols) or float32 partial sums [parts, tokens, cols] plus ``bias`` (float32 [cols]); every q
-    and k head divided by its root mean square (``head_norm``, no gain); the first ``rotary_dim`` elements of
+    and k head divided by its root mean square (``head_norm``; times ``q_gain`` / ``k_gain`` when given); the first ``rotary_dim`` elements of
     every q and k head rotated with ``cos_sin`` [positions, rotary_dim / 2, 2], pairs (i, i + rotary_dim / 2)
     ("half") or (2i, 2i + 1) ("interleaved"); v <- (1 - mix) v + mix v_first with ``mix`` a float32 scalar on
     the device and ``v_first`` float32 (tokens, n_kv * v_dim); ``v_keep`` (float32, contiguous) takes this layer's
@@ -553,6 +567,8 @@ def qkv_finish(proj: torch.Tensor, bias: Optional[torch.Tensor], n_q: int, n_kv:
         ld_first = v_first.stride(0)
     if v_keep is not None:
         assert v_keep.dtype == torch.float32 and v_keep.is_contiguous() and v_keep.shape == (out.shape[0], n_kv * v_dim)
+    for gain in (q_gain, k_gain):              # float32 [head_dim]: multiplies every normed head of its kind
+        assert gain is None or (head_norm and gain.dtype == torch.float32 and gain.is_contiguous() and gain.numel() == head_dim)
     if k_pages is not None:
         assert v_pages is not None and cache_rows is not None and k_pages.dtype == out.dtype and v_pages.dtype == out.dtype
         assert k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -562,12 +578,12 @@ def qkv_finish(proj: torch.Tensor, bias: Optional[torch.Tensor], n_q: int, n_kv:
     f = _fn("headwise", "brolm_qkv_finish", [c_void_p, c_int, c_int, c_longlong, c_long, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                              c_long, c_void_p, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p,
-                                             c_int, c_int, c_void_p])
+                                             c_int, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(proj), _code(proj), parts, part_stride, proj.stride(-2), _ptr(bias), n_q, n_kv, head_dim, v_dim,
              1 if head_norm else 0, eps, _ptr(positions), _ptr(cos_sin), rotary_dim, ROPE_PAIRINGS[pairing],
              _ptr(mix) if v_first is not None else None, _ptr(v_first), ld_first, _ptr(v_keep), _ptr(out), _code(out),
              out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows) if k_pages is not None else None, page_size,
-             out.shape[0], _stream()), "qkv_finish")
+             out.shape[0], _ptr(q_gain), _ptr(k_gain), _stream()), "qkv_finish")
 
 
 def heads_mix(acc: torch.Tensor, talk: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
@@ -645,10 +661,11 @@ def gate_group_norm(y: torch.Tensor, z: torch.Tensor, gain: torch.Tensor, eps: f
 
 
 def experts_combine(y: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor, n_real: int, x: torch.Tensor,
-                    shared: Optional[torch.Tensor], out: torch.Tensor) -> None:
+                    shared: Optional[torch.Tensor], out: torch.Tensor, shared_gate: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum over t's choices c of weights[t, c] * (y[c, t] if ids[t, c] < n_real else x[t]) + shared[t].
     y float32 [top, tokens, hidden] (None when there is no real expert); shared float32 (tokens, hidden) or
-    [parts, tokens, hidden], or None."""
+    [parts, tokens, hidden], or None.  ``shared_gate`` (hidden numbers of x's type): the shared result is multiplied
+    by sigmoid(shared_gate . x[t]), one number per token."""
     tokens, top = ids.shape
     hidden = out.shape[1]
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
@@ -661,10 +678,25 @@ def experts_combine(y: Optional[torch.Tensor], ids: torch.Tensor, weights: torch
     if shared is not None:
         assert shared.dtype == torch.float32 and shared.is_contiguous() and tuple(shared.shape[-2:]) == (tokens, hidden)
         sp, sstr = (shared.shape[0], shared.stride(0)) if shared.dim() == 3 else (1, 0)
+    if shared_gate is not None:
+        assert shared_gate.dtype == x.dtype and shared_gate.is_contiguous() and shared_gate.numel() == hidden
+        assert x.shape[1] == hidden
     f = _fn("rowwise", "brolm_experts_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_long,
-                                                 c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p])
+                                                 c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(y), _ptr(ids), _ptr(weights), top, n_real, _ptr(x), _code(x), x.stride(0), _ptr(shared), sp, sstr,
-             _ptr(out), tokens, hidden, _stream()), "experts_combine")
+             _ptr(out), tokens, hidden, _ptr(shared_gate), _stream()), "experts_combine")
+
+
+def norm_sigmoid_gate(y: torch.Tensor, z: torch.Tensor, gain: Optional[torch.Tensor], eps: float, out: torch.Tensor) -> None:
+    """out = n(y) * sigmoid(z) row by row: n(y) = y * rsqrt(mean(y^2) + eps) * gain over the whole row, or y itself
+    when ``gain`` is None.  y, z (tokens, cols), possibly strided views; float arithmetic."""
+    tokens, cols = y.shape
+    assert z.shape == y.shape and out.shape == y.shape and y.stride(1) == 1 and z.stride(1) == 1 and out.stride(1) == 1
+    assert gain is None or (gain.is_contiguous() and gain.numel() == cols)
+    f = _fn("rowwise", "brolm_norm_sigmoid_gate", [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_float,
+                                                   c_int, c_void_p, c_int, c_long, c_int, c_void_p])
+    _check(f(_ptr(y), _code(y), y.stride(0), _ptr(z), _code(z), z.stride(0), _ptr(gain), _code(gain) if gain is not None else F32,
+             eps, cols, _ptr(out), _code(out), out.stride(0), tokens, _stream()), "norm_sigmoid_gate")
 
 
 # --- mixers with a state (csrc/recurrent.cu) --------------------------------
@@ -787,6 +819,35 @@ def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
     _check(f(_ptr(xbc), xbc.stride(0), _ptr(dt_raw), _code(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(d),
              heads, groups, P, N, *_seq(cu_q, kv_len, slots, state), _ptr(y), y.stride(0), batch, max_q_len, _stream()),
            "ssm_scan")
+
+
+SCAN_ACTS = {"none": 0, "silu": 1}
+
+
+def decay_state_size(heads: int, dim: int, v_dim: int) -> int:
+    """Floats of a sequence's state row that ``decay_scan`` keeps: [head][value column][dim padded to four]."""
+    return heads * v_dim * ((dim + 3) // 4 * 4)
+
+
+def decay_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int, v_dim: int, activation: str,
+               decay_m1: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
+               out: torch.Tensor, batch: int) -> None:
+    """Linear attention with a fixed decay per head over the packed tokens: S <- decay_h S + k v^T, out = S^T q.
+    q, k (``dim`` per head) and v (``v_dim`` per head) are columns of ``qkv`` (tokens, cols) from ``q_off``, ``k_off``,
+    ``v_off`` on, head by head; ``activation`` ("none", "silu") is applied to them as they are read.  ``decay_m1``
+    float32 [heads] holds decay - 1.  S is the first ``decay_state_size`` floats of ``state[slot]``.  ``out`` float32
+    (tokens, heads * v_dim)."""
+    assert qkv.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (qkv.shape[0], heads * v_dim)
+    assert decay_m1.dtype == torch.float32 and decay_m1.is_contiguous() and decay_m1.numel() == heads
+    assert max(q_off, k_off) + heads * dim <= qkv.shape[1] and v_off + heads * v_dim <= qkv.shape[1]
+    assert state.shape[1] >= decay_state_size(heads, dim, v_dim)
+    if activation not in SCAN_ACTS:
+        raise KernelError(f"decay_scan: unknown activation '{activation}'")
+    f = _fn("linear_attn", "brolm_decay_scan", [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long,
+                                                c_int, c_void_p])
+    _check(f(_ptr(qkv), _code(qkv), qkv.stride(0), q_off, k_off, v_off, heads, dim, v_dim, SCAN_ACTS[activation],
+             _ptr(decay_m1), *_seq(cu_q, kv_len, slots, state), _ptr(out), out.stride(0), batch, _stream()), "decay_scan")
 
 
 def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -1117,7 +1178,7 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
                    page_table: Optional[torch.Tensor] = None, ring: int = 0, page_size: int = 0,
                    sink: Optional[torch.Tensor] = None, v_dim: Optional[int] = None, chunk: int = 0,
                    slopes: Optional[torch.Tensor] = None, keep_first: int = 0, ring_from: int = 0,
-                   v_all: int = 0, v_from: int = 0) -> None:
+                   v_all: int = 0, v_from: int = 0, dist_bias: Optional[torch.Tensor] = None) -> None:
     """Exact attention on CUDA cores.  Keys come from (k, v) packed like q, or from cache pages.
     ``sink``: float32 [query heads]; exp(sink) joins every softmax's denominator (a key with no value).
     ``v_dim``: size of a value row and of an output row when it is not ``head_dim``.
@@ -1128,7 +1189,10 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
     ``v_all`` > 0: every query head's weights are applied to the value rows of ``v_all`` kv heads from
     ``v_from`` on; ``out`` is then (tokens, heads * n_kv * v_dim), head h's row being [n_kv][v_dim], of which
     the call fills those kv heads' part (``attention_all_values`` covers all of them).
-    ``out`` may be float32 whatever the element type of q."""
+    ``out`` may be float32 whatever the element type of q.
+    ``dist_bias``: float32 [query heads, L]; key j adds entry min(p - j, L - 1) of its head's row to the score
+    after the scale and the cap."""
+    _check_dist_bias(dist_bias, n_kv * group)
     _check_sink(sink, n_kv * group)
     _check_sink(slopes, n_kv * group)
     vd = v_dim or head_dim
@@ -1149,11 +1213,13 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
     f = _fn("attn_simt", "brolm_attn_simt", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int,
-                                             c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                             c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                             c_int, c_void_p])
     _check(f(_code(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k), _ptr(v),
              kv_stride, _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, ring, page_size, n_kv, group,
              head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, vd, v_stride, int(chunk), _ptr(slopes),
-             int(keep_first), int(ring_from), int(v_all), int(v_from), 1 if out.dtype == torch.float32 else 0, _stream()),
+             int(keep_first), int(ring_from), int(v_all), int(v_from), 1 if out.dtype == torch.float32 else 0,
+             _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _stream()),
            "attention_simt")
 
 
@@ -1264,6 +1330,12 @@ def attention_headmix_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Ten
              page_size, n_kv, group, head_dim, v_dim, scale, int(window), int(keep_first), _ptr(slopes),
              1 if all_values else 0, batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()),
            "attention_headmix_decode")
+
+
+def _check_dist_bias(table: Optional[torch.Tensor], n_q: int) -> None:
+    if table is not None:
+        assert table.dtype == torch.float32 and table.is_contiguous() and table.dim() == 2 and table.shape[0] == n_q
+        assert table.shape[1] >= 1
 
 
 def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:

@@ -49,6 +49,7 @@ LIBRARIES: dict[str, list[str]] = {
     "headwise": ["headwise.cu"],
     "attn_headmix": ["attn_headmix.cu"],
     "groupnorm": ["groupnorm.cu"],
+    "linear_attn": ["linear_attn.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
 

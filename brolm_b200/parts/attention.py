@@ -27,7 +27,18 @@ head h reads kv head h // (H / G)):
   sequence's start), whose last K - 1 inputs are kept per sequence in a state
   entry beside the keys and values;
 * ``qk_norm="head"``: every q and k head divided by its own root mean square
-  (``eps``), no gain;
+  (``eps``), no gain; with ``qk_gain`` the normed heads are multiplied by a gain of
+  ``head_dim`` numbers, one for all query heads (tensor ``q_norm``) and one for
+  all key heads (``k_norm``);
+* ``sink``: a learned number per query head (tensor ``sink``) whose exponential
+  joins the softmax's denominator: it has no key and no value, and is neither
+  scaled nor capped;
+* ``distance_rows`` = B > 0 with ``distance_far`` = D: a learned bias by distance
+  (tensor ``rel``, B rows of one number per query head) is added to the score
+  after the scale and the cap; key j at distance n = p - j reads row n for
+  n < B/2, else min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(D / (B/2)) (B - B/2)));
+  with ``distance_rows_free`` B is whatever the checkpoint's tensor has, and
+  ``distance_rows`` only says how many rows a tensor made at random gets;
 * a rotation of part of a head, in either pairing, also with ``v_dim``;
 * ``slope_power`` = s > 0: slope_h * (p - j) is taken off the scaled score of
   key j at query position p, slope_h = 2^(-s (h + 1) / H);
@@ -49,6 +60,7 @@ head h reads kv head h // (H / G)):
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -59,6 +71,23 @@ from .base import ParamSpec, Part, register_part
 from .linear import linear
 
 
+def distance_buckets(rows: int, far: float) -> list:
+    """The row of a distance-bias table that each distance n = 0, 1, ... reads, up to and including the first
+    distance that reads the last row (every larger one reads it too): n itself below rows // 2, then steps that
+    grow like the logarithm of n, reaching the last row at ``far``."""
+    half = rows // 2
+    out, n = [], 0
+    while True:
+        if n < half:
+            b = n
+        else:
+            b = min(rows - 1, half + math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))
+        out.append(b)
+        if b == rows - 1:
+            return out
+        n += 1
+
+
 class Attention(Part):
     kind = "mixer"
     graph_safe = True
@@ -67,11 +96,13 @@ class Attention(Part):
                  window: Optional[int] = None, position: Optional[Part] = None, v_dim: Optional[int] = None,
                  qk_norm: str = "none", eps: float = 0.0, chunk: Optional[int] = None, bias: bool = False, taps: int = 0,
                  slope_power: float = 0.0, keep_first: int = 0, talk: bool = False, gate: bool = False,
-                 v_mix: Optional[str] = None, v_mix_key: str = "v_first"):
+                 v_mix: Optional[str] = None, v_mix_key: str = "v_first", qk_gain: bool = False, sink: bool = False,
+                 distance_rows: int = 0, distance_far: float = 0.0, distance_rows_free: bool = False):
         if n_q % n_kv:
             raise ValueError("attention: the number of query heads must be a multiple of the kv heads")
         rotation = getattr(position, "pairing", "half")
         self.headwise = bool(bias or taps or qk_norm == "head" or slope_power or keep_first or talk or gate or v_mix
+                             or sink or distance_rows
                              or (position is not None and ((v_dim and v_dim != head_dim) or rotation != "half")))
         plain = not (v_dim and v_dim != head_dim) and qk_norm == "none" and not chunk and not self.headwise
         if plain and head_dim % 16:
@@ -86,8 +117,16 @@ class Attention(Part):
             raise ValueError("attention: taps, keep_first and slope_power cannot be negative")
         if keep_first and not window:
             keep_first = 0                    # every key is visible anyway
-        if self.headwise and (qk_norm == "whole" or softcap):
-            raise ValueError("attention: a whole-row norm or a soft cap together with the head-wise options is not built")
+        if self.headwise and qk_norm == "whole":
+            raise ValueError("attention: a whole-row norm together with the head-wise options is not built")
+        if self.headwise and softcap and talk:
+            raise ValueError("attention: a soft cap together with mixed heads' weights is not built")
+        if qk_gain and qk_norm != "head":
+            raise ValueError("attention: a gain per head element goes with qk_norm='head'")
+        if distance_rows < 0 or (distance_rows and (distance_rows < 2 or not distance_far > distance_rows // 2)):
+            raise ValueError("attention: the distance bias needs at least two rows and distance_far beyond half of them")
+        if (sink or distance_rows) and talk:
+            raise ValueError("attention: a sink or a distance bias together with mixed heads' weights is not built")
         if keep_first and chunk:
             raise ValueError("attention: kept first keys together with a chunked mask are not built")
         self.hidden, self.n_q, self.n_kv, self.head_dim = hidden, n_q, n_kv, head_dim
@@ -101,6 +140,9 @@ class Attention(Part):
         # the options of the second paragraph above: their own row-wise kernel and the exact attention
         self.bias, self.taps, self.slope_power, self.keep_first = bool(bias), int(taps), float(slope_power), int(keep_first)
         self.talk, self.gate, self.v_mix, self.v_mix_key = bool(talk), bool(gate), v_mix, v_mix_key
+        self.qk_gain, self.has_sink = bool(qk_gain), bool(sink)
+        self.distance_rows, self.distance_far = int(distance_rows), float(distance_far)
+        self.distance_rows_free = bool(distance_rows_free)
         self.cols = self.q_dim + self.kv_dim + self.v_cols
         self.slopes = None
         self.rowwise = (self.v_dim != head_dim or qk_norm != "none" or self.chunk is not None) and not self.headwise
@@ -118,6 +160,14 @@ class Attention(Part):
         if self.qk_norm == "whole":
             specs["q_norm"] = ParamSpec((self.q_dim,), "vector")
             specs["k_norm"] = ParamSpec((self.kv_dim,), "vector")
+        if self.qk_gain:
+            specs["q_norm"] = ParamSpec((self.head_dim,), "vector")
+            specs["k_norm"] = ParamSpec((self.head_dim,), "vector")
+        if self.has_sink:
+            specs["sink"] = ParamSpec((self.n_q,), "vector")
+        if self.distance_rows:
+            specs["rel"] = ParamSpec((-self.distance_rows if self.distance_rows_free else self.distance_rows, self.n_q),
+                                     "vector")
         if self.bias:
             specs.update(q_bias=ParamSpec((self.q_dim,), "vector"), k_bias=ParamSpec((self.kv_dim,), "vector"),
                          v_bias=ParamSpec((self.v_cols,), "vector"), o_bias=ParamSpec((self.hidden,), "vector"))
@@ -148,6 +198,18 @@ class Attention(Part):
         self.w_talk = params["talk"].float().contiguous() if self.talk else None
         self.lam = params["vmix"].float().reshape(1).contiguous() if self.v_mix == "mixed" else None
         self.q_gain = self.k_gain = None
+        if self.qk_gain:
+            self.q_gain, self.k_gain = params["q_norm"].float().contiguous(), params["k_norm"].float().contiguous()
+        self.sink = params["sink"].float().contiguous() if self.has_sink else None
+        self.dist_bias = None
+        if self.distance_rows:
+            # laid out by distance: [head][n] for n up to the first distance that reads the last row (all further do)
+            n_rows = params["rel"].shape[0]
+            if n_rows < 2 or not self.distance_far > n_rows // 2:
+                raise ValueError(f"attention: a distance bias of {n_rows} rows does not go with distance_far "
+                                 f"{self.distance_far}")
+            rows = torch.tensor(distance_buckets(n_rows, self.distance_far), device=params["rel"].device)
+            self.dist_bias = params["rel"].float().index_select(0, rows).t().contiguous()
         if self.qk_norm == "whole":
             gd = torch.float32 if params["q_norm"].dtype != params["k_norm"].dtype else params["q_norm"].dtype
             self.q_gain, self.k_gain = params["q_norm"].to(gd).contiguous(), params["k_norm"].to(gd).contiguous()
@@ -281,14 +343,15 @@ class Attention(Part):
                            cos_sin=pos.table if pos is not None else None,
                            rotary_dim=pos.rotary_dim if pos is not None else 0,
                            pairing=pos.pairing if pos is not None else "half", mix=mix, v_first=v_first, v_keep=v_keep,
-                           k_pages=k_pages, v_pages=v_pages, cache_rows=ctx.cache_rows[kv_entry.group_id], page_size=page)
+                           q_gain=self.q_gain, k_gain=self.k_gain, k_pages=k_pages, v_pages=v_pages, cache_rows=ctx.cache_rows[kv_entry.group_id], page_size=page)
         q = qkv[:, :self.q_dim]
         k, v = qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
         group = self.n_q // self.n_kv
-        common = dict(n_kv=self.n_kv, group=group, head_dim=self.head_dim, scale=self.scale, cap=0.0,
+        common = dict(n_kv=self.n_kv, group=group, head_dim=self.head_dim, scale=self.scale, cap=self.softcap,
                       window=self.window or 0, batch=ctx.batch, max_q_len=ctx.max_q_len)
         out = torch.empty((T, self.n_q * self.v_dim), dtype=ctx.dtype, device=dev)
-        special = self.talk or self.gate or self.slopes is not None or self.keep_first or self.chunk
+        scored = bool(self.softcap or self.has_sink or self.dist_bias is not None)     # options of the score itself
+        special = self.talk or self.gate or self.slopes is not None or self.keep_first or self.chunk or scored
         if not special and self.v_dim == self.head_dim and self.head_dim % 16 == 0 and self._tensor_cores(ctx):
             # nothing the tensor-core kernels do not know: the same attention as a plain layer's
             if ctx.mode == "prefill":
@@ -296,14 +359,15 @@ class Attention(Part):
             else:
                 self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
         else:
-            exact = dict(common, v_dim=self.v_dim, chunk=self.chunk or 0, slopes=self.slopes, keep_first=self.keep_first)
+            exact = dict(common, v_dim=self.v_dim, chunk=self.chunk or 0, slopes=self.slopes, keep_first=self.keep_first,
+                         sink=self.sink, dist_bias=self.dist_bias)
             if ctx.mode == "prefill":
                 source = dict(k=k, v=v)
             else:
                 source = dict(k_pages=k_pages, v_pages=v_pages, page_table=table, ring=ring, page_size=page,
                               ring_from=ctx.ring_from(kv_entry))
             # bfloat16 without a chunked mask runs on the tensor cores, all else on the exact kernel
-            tensor = self._tensor_cores(ctx) and not self.chunk and \
+            tensor = self._tensor_cores(ctx) and not self.chunk and not scored and \
                 kernels.attention_headmix_ok(self.head_dim, self.v_dim, group, ctx.mode != "prefill", page)
 
             def attend(dst, all_values=False):

@@ -22,7 +22,8 @@ KINDS = ("mixer", "feedforward", "norm", "position", "block", "stream")
 class ParamSpec:
     """One tensor a part needs.  ``role``: ``matrix`` (a projection, (out, in)),
     ``vector`` (a gain or bias), ``table`` (looked up by index), ``int`` (an
-    integer table, kept as int32)."""
+    integer table, kept as int32).  A negative entry of ``shape`` leaves that size to the checkpoint's tensor; its
+    magnitude is the size a tensor made at random gets."""
     shape: tuple
     role: str = "matrix"
 

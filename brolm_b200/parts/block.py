@@ -97,14 +97,18 @@ register_part("block", "sandwich", Block)
 
 class ParallelBlock(Part):
     """h += mixer(n1(h)) + ffn(n2(h)): both sublayers read the same stream, each through a norm of its own,
-    and the stream takes both results at once.  Without a feed-forward it is h += mixer(n1(h))."""
+    and the stream takes both results at once.  Without a feed-forward it is h += mixer(n1(h)).  With
+    ``one_norm`` there is no second norm: h += mixer(n1(h)) + ffn(n1(h)), both sublayers read the same rows."""
 
     kind = "block"
 
     def __init__(self, mixer: Part, pre_mixer_norm: Part, feedforward: Optional[Part] = None,
-                 pre_ffn_norm: Optional[Part] = None):
-        if (feedforward is None) != (pre_ffn_norm is None):
+                 pre_ffn_norm: Optional[Part] = None, one_norm: bool = False):
+        if one_norm and pre_ffn_norm is not None:
+            raise ValueError("block: with one norm for both sublayers there is no norm of the feed-forward's own")
+        if not one_norm and (feedforward is None) != (pre_ffn_norm is None):
             raise ValueError("block: a feed-forward and its norm come together")
+        self.one_norm = bool(one_norm)
         self.mixer, self.feedforward = mixer, feedforward
         self.pre_mixer_norm, self.pre_ffn_norm = pre_mixer_norm, pre_ffn_norm
 
@@ -123,7 +127,7 @@ class ParallelBlock(Part):
                 next_norm: Optional[Part]) -> Optional[torch.Tensor]:
         if self.feedforward is None:
             return add_then_norm(h, self.mixer.forward(x, ctx, entry, writes_cache), None, next_norm, ctx.dtype)
-        x2 = self.pre_ffn_norm.apply(h, ctx.dtype)            # of the stream as the layer found it
+        x2 = x if self.one_norm else self.pre_ffn_norm.apply(h, ctx.dtype)     # of the stream as the layer found it
         y = self.mixer.forward(x, ctx, entry, writes_cache)
         y2 = self.feedforward.forward(x2, ctx)
         add_then_norm(h, y, None, None, ctx.dtype)
@@ -131,6 +135,16 @@ class ParallelBlock(Part):
 
 
 register_part("block", "parallel", ParallelBlock)
+
+
+class OneNormParallelBlock(ParallelBlock):
+    """The parallel arrangement with a single norm: h += mixer(n(h)) + ffn(n(h))."""
+
+    def __init__(self, mixer: Part, pre_mixer_norm: Part, feedforward: Optional[Part] = None):
+        super().__init__(mixer, pre_mixer_norm, feedforward, None, one_norm=True)
+
+
+register_part("block", "parallel_one_norm", OneNormParallelBlock)
 
 
 class PostNormBlock(Part):

@@ -33,7 +33,12 @@ class RoutedExperts(Part):
       gate and up run as one grouped product over the rows [W_gate; W_up];
     * ``identity`` = n: the router has n more outputs, after the experts'; a token that chooses one of them
       gets its own input back (times the weight).  They have no tensors and take no part in the products;
-    * ``shared``: a feed-forward part that every token runs; its result is added.
+    * ``shared``: a feed-forward part that every token runs; its result is added; with ``shared_gate`` it is first
+      multiplied by sigmoid(w_sg . x), one number per token (tensor ``shared_gate``, one row);
+    * ``groups`` = (count, keep) with the softmax router: the experts form ``count`` equal groups of neighbours, a
+      group's score is its largest s (+ correction), and only experts of the ``keep`` best groups can be chosen;
+    * ``renorm=False`` with the softmax router: the weights are the chosen s themselves, not divided by their sum;
+    * ``weight_scale``: a constant that multiplies the weights.
 
     The result of that form is one float32 (tokens, hidden) array: weights, identity experts and the shared
     expert are folded in by one row-wise kernel.
@@ -44,7 +49,21 @@ class RoutedExperts(Part):
 
     def __init__(self, hidden: int, inter: int, experts: int, top: int, activation: str = "relu2",
                  scale_input: bool = True, router: str = "logistic", correction: bool = False, gated: bool = False,
-                 identity: int = 0, shared: Optional[Part] = None):
+                 identity: int = 0, shared: Optional[Part] = None, shared_gate: bool = False, groups=None,
+                 renorm: bool = True, weight_scale: float = 1.0):
+        count, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+        if (count, keep) != (1, 1) or not renorm or float(weight_scale) != 1.0:
+            if router != "softmax":
+                raise ValueError("routed experts: groups, unnormalised weights and a weight scale go with the softmax router")
+            if identity:
+                raise ValueError("routed experts: groups or unnormalised weights together with identity experts are not built")
+            if count < 1 or not 1 <= keep <= count or experts % count or top > keep * (experts // count):
+                raise ValueError(f"routed experts: {experts} experts in {count} groups of which {keep} stay open cannot "
+                                 f"give {top} choices")
+        if shared_gate and shared is None:
+            raise ValueError("routed experts: a gate of the shared expert needs a shared expert")
+        self.groups, self.keep, self.renorm, self.weight_scale = count, keep, bool(renorm), float(weight_scale)
+        self.has_shared_gate = bool(shared_gate)
         if experts < 0 or identity < 0 or not 1 <= top <= experts + identity:
             raise ValueError("routed experts: 1 <= top <= experts + identity")
         if router not in kernels.ROUTE_MODES:
@@ -52,6 +71,8 @@ class RoutedExperts(Part):
         if correction and router != "softmax":
             raise ValueError("routed experts: a correction of the choice goes with the softmax router")
         self.weighted = bool(router != "logistic" or not scale_input or gated or identity or shared is not None)
+        self.route_opts = dict(groups=count, keep=keep, renorm=bool(renorm), scale=float(weight_scale)) \
+            if router == "softmax" else {}
         if self.weighted:
             if scale_input:
                 raise ValueError("routed experts: with these options the weight goes on the expert's result "
@@ -73,6 +94,8 @@ class RoutedExperts(Part):
         specs = {"router": ParamSpec((self.experts + self.identity, self.hidden))}
         if self.has_correction:
             specs["correction"] = ParamSpec((self.experts + self.identity,), "vector")
+        if self.has_shared_gate:
+            specs["shared_gate"] = ParamSpec((1, self.hidden))
         for e in range(self.experts):
             if self.gated:
                 specs[f"e{e}.gate"] = ParamSpec((self.inter, self.hidden))
@@ -87,6 +110,8 @@ class RoutedExperts(Part):
         if len(kinds) > 1:
             raise TypeError("routed experts: the experts' matrices and the router must have one element type")
         self.correction = params["correction"].float().contiguous() if self.has_correction else None
+        self.w_shared_gate = params["shared_gate"].to(self.router.dtype).reshape(-1).contiguous() \
+            if self.has_shared_gate else None
         if self.experts:
             if self.gated:      # per expert the rows [W_gate; W_up]
                 self.w_up = torch.stack([torch.cat([params[f"e{e}.gate"], params[f"e{e}.up"]], dim=0)
@@ -102,9 +127,9 @@ class RoutedExperts(Part):
             # a prompt: the scores as one matrix product (bfloat16 products are exact in float, the sums are
             # float), then the choice; the router kernel's float multiply-adds are what bounds it from here on
             kernels.route_pick(linear(x, self.router, out_dtype=torch.float32), self.top, ids, gates, self.route_mode,
-                               self.correction)
+                               self.correction, **self.route_opts)
         else:
-            kernels.route_topk(x, self.router, self.top, ids, gates, self.route_mode, self.correction)
+            kernels.route_topk(x, self.router, self.top, ids, gates, self.route_mode, self.correction, **self.route_opts)
 
     def _forward_weighted(self, x: torch.Tensor, ctx) -> torch.Tensor:
         """x (tokens, hidden) -> (tokens, hidden) float32: the weighted sum of the chosen experts' results,
@@ -143,7 +168,7 @@ class RoutedExperts(Part):
                 kernels.experts_linear(u, self.w_down, y, perm, offsets, tiles, self.top, T, down=True)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
-        kernels.experts_combine(y, ids, gates, E, x, shared, out)
+        kernels.experts_combine(y, ids, gates, E, x, shared, out, self.w_shared_gate)
         return out
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:

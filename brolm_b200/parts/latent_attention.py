@@ -10,6 +10,10 @@ dv value entries; R the latent's size):
     s_h(i, j) = (q_n,h(i) . k_n,h(j) + rot(q_r,h(i), i) . rot(k_r(j), j)) * scale,   0 <= i - j < window
     p = softmax over j with exp(sink_h) added to the denominator;   o_h = sum_j p v_h(j);   y = W_o [o_1 .. o_H]
 
+Without ``sink`` the softmax is the ordinary one.  With ``gate`` the heads' results are multiplied element by element
+by sigmoid(W_g h) before the output product: y = W_o ([o_1 .. o_H] * sigmoid(W_g h)), W_g being further rows of the
+input product.
+
 Only [c | rot(k_r)] is cached, one row of R + dr entries per token, and attention runs in the latent's
 space: since q_n . (W_uk c) = (W_uk^T q_n) . c, every head's query becomes [W_uk,h^T q_n,h | rot(q_r,h)] and
 all heads share the cached row as their key; the weighted sum of cached rows is projected up by W_uv,h
@@ -37,7 +41,9 @@ class LatentAttention(Part):
     graph_safe = True
 
     def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
-                 eps: float, window: Optional[int] = None, sink: bool = True, position: Optional[Part] = None):
+                 eps: float, window: Optional[int] = None, sink: bool = True, position: Optional[Part] = None,
+                 gate: bool = False):
+        self.has_gate = bool(gate)
         self.hidden, self.heads, self.dn, self.dr, self.dv, self.rank = hidden, heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps = float(scale), float(eps)
         self.window = int(window) if window else None
@@ -57,14 +63,17 @@ class LatentAttention(Part):
                  "uv": ParamSpec((self.heads * self.dv, self.rank)), "o": ParamSpec((self.hidden, self.heads * self.dv))}
         if self.has_sink:
             specs["sink"] = ParamSpec((self.heads,), "vector")
+        if self.has_gate:
+            specs["g"] = ParamSpec((self.heads * self.dv, self.hidden))
         return specs
 
     def bind(self, params):
-        kinds = {params[n].dtype for n in ("q", "dkv", "uk", "uv", "dkv_norm")}
+        kinds = {params[n].dtype for n in ("q", "dkv", "uk", "uv", "dkv_norm") + (("g",) if self.has_gate else ())}
         if len(kinds) > 1:
             raise TypeError("latent attention: its matrices and the latent's gain must have one element type")
-        # one product for the queries and the compressed row: rows [Wq; Wdkv]
-        self.w_in = torch.cat([params["q"], params["dkv"]], dim=0).contiguous()
+        # one product for the queries, the compressed row and the gate's logits: rows [Wq; Wdkv; Wg]
+        self.w_in = torch.cat([params["q"], params["dkv"]] + ([params["g"]] if self.has_gate else []), dim=0).contiguous()
+        self.gate_from = self.q_cols + self.rank + self.dr
         self.gain = params["dkv_norm"].contiguous()
         # per head: W_uk^T (R, dn) for the queries' way into the latent's space, W_uv (dv, R) for the way out
         self.w_qk = params["uk"].view(self.heads, self.dn, self.rank).transpose(1, 2).contiguous()
@@ -122,6 +131,10 @@ class LatentAttention(Part):
                                    ring=ring, page_size=page, max_q_len=ctx.max_q_len, **common)
         o = torch.empty((T, H * self.dv), dtype=x.dtype, device=x.device)
         kernels.heads_linear(out, D, self.w_uv, o, self.dv)
+        if self.has_gate:
+            gated = torch.empty_like(o)
+            kernels.norm_sigmoid_gate(o, proj[:, self.gate_from:], None, 0.0, gated)
+            o = gated
         return linear(o, self.w_o, out_dtype=torch.float32, parts_ok=True)
 
 

@@ -181,6 +181,81 @@ class StateSpace(Part):
 register_part("mixer", "state_space", StateSpace)
 
 
+class DecayLinearAttention(Part):
+    """Linear attention with one fixed decay per head ("lightning" attention).
+
+    q = act(W_q x), k = act(W_k x) (``heads`` x ``dim``) and v = act(W_v x) (``heads`` x ``v_dim``), laid out head by
+    head; per head S <- decay_h S + k v^T and o = S^T q, with no other scale.  The heads' results together pass an
+    RMS norm over the whole row with a gain (``norm``), are multiplied by sigmoid(W_g x) (``gate``) and go through
+    W_o.  ``decay``: one number per head.  The projection's sums, the activation, S and the norm are float32 in
+    every mode; S is a state row per sequence, zero at the sequence's start."""
+
+    kind = "mixer"
+    graph_safe = True
+
+    def __init__(self, hidden: int, heads: int, dim: int, v_dim: int, decay, eps: float, activation: str = "silu",
+                 norm: bool = True, gate: bool = True):
+        decay = [float(d) for d in decay]
+        if len(decay) != heads:
+            raise ValueError(f"decay attention: {len(decay)} decays for {heads} heads")
+        if any(not 0.0 <= d <= 1.0 for d in decay):
+            raise ValueError("decay attention: every decay lies between 0 and 1")
+        if activation not in kernels.SCAN_ACTS:
+            raise ValueError(f"decay attention: unknown activation '{activation}'")
+        if dim > 512:
+            raise ValueError("decay attention: more than 512 query/key entries per head are beyond the kernel")
+        self.hidden, self.heads, self.dim, self.v_dim, self.decay = hidden, heads, dim, v_dim, decay
+        self.eps, self.activation, self.has_norm, self.has_gate = float(eps), activation, bool(norm), bool(gate)
+        self.qk_cols, self.v_cols = heads * dim, heads * v_dim
+
+    def param_specs(self):
+        specs = {"q": ParamSpec((self.qk_cols, self.hidden)), "k": ParamSpec((self.qk_cols, self.hidden)),
+                 "v": ParamSpec((self.v_cols, self.hidden)), "o": ParamSpec((self.hidden, self.v_cols))}
+        if self.has_gate:
+            specs["g"] = ParamSpec((self.v_cols, self.hidden))
+        if self.has_norm:
+            specs["norm"] = ParamSpec((self.v_cols,), "vector")
+        return specs
+
+    def bind(self, params):
+        names = ("q", "k", "v") + (("g",) if self.has_gate else ())
+        kinds = {params[n].dtype for n in names}
+        dt = torch.float32 if (len(kinds) > 1 or torch.float32 in kinds) else next(iter(kinds))
+        # one product for q, k, v and the gate's logits: rows [Wq; Wk; Wv; Wg]
+        self.w_in = torch.cat([params[n].to(dt) for n in names], dim=0).contiguous()
+        self.w_o = params["o"]
+        self.gain = params["norm"].contiguous() if self.has_norm else None
+        # decay - 1, taken in double: what a float keeps of it is far finer than what it keeps of the decay itself
+        self.decay_m1 = torch.tensor([d - 1.0 for d in self.decay], dtype=torch.float64).to(torch.float32) \
+            .to(self.w_in.device)
+        self.params = {}
+
+    def cache_spec(self):
+        return StateSpec((kernels.decay_state_size(self.heads, self.dim, self.v_dim),), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, entry, writes_cache: bool = True) -> torch.Tensor:
+        """x (tokens, hidden) -> (tokens, hidden) float32, or partial sums [parts, tokens, hidden]."""
+        if not writes_cache:
+            raise NotImplementedError("a mixer with a state cannot run on another layer's state")
+        T = x.shape[0]
+        proj = linear(x, self.w_in, out_dtype=torch.float32)              # [ q | k | v | gate logits ]
+        y = torch.empty((T, self.v_cols), dtype=torch.float32, device=x.device)
+        kernels.decay_scan(proj, 0, self.qk_cols, 2 * self.qk_cols, self.heads, self.dim, self.v_dim, self.activation,
+                           self.decay_m1, ctx.cu_q, ctx.kv_len, ctx.slots_dev, ctx.state(entry), y, ctx.batch)
+        if self.has_norm or self.has_gate:
+            out = torch.empty((T, self.v_cols), dtype=ctx.dtype, device=x.device)
+            if self.has_gate:
+                kernels.norm_sigmoid_gate(y, proj[:, 2 * self.qk_cols + self.v_cols:], self.gain, self.eps, out)
+            else:
+                kernels.rmsnorm(y, self.gain, self.eps, 0.0, out)
+        else:
+            out = y if ctx.dtype == torch.float32 else y.to(ctx.dtype)
+        return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
+
+
+register_part("mixer", "decay_attention", DecayLinearAttention)
+
+
 class SideBySide(Part):
     """Two mixers that read the same input; the result is left_scale * left + right_scale * right.
     Each keeps what it keeps: the pair's cache spec is the tuple of both."""

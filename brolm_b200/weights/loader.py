@@ -26,6 +26,12 @@ class WeightsError(ValueError):
         self.missing, self.unexpected, self.wrong_shape = list(missing), list(unexpected), list(wrong_shape)
 
 
+def shape_fits(expected: tuple, got: tuple) -> bool:
+    """A negative entry of an expected shape leaves that size to the tensor (its magnitude is the size a tensor made
+    at random gets); every other entry must be met."""
+    return len(expected) == len(got) and all((e < 0 and g >= 1) or e == g for e, g in zip(expected, got))
+
+
 @dataclasses.dataclass
 class Expected:
     shape: tuple
@@ -48,7 +54,7 @@ def check_names(expected: dict[str, Expected], present: dict[str, tuple], where:
     missing = [n for n, e in expected.items() if n not in present and not e.optional]
     unexpected = [n for n in present if n not in expected]
     wrong = [(n, tuple(expected[n].shape), tuple(present[n])) for n in expected
-             if n in present and tuple(present[n]) != tuple(expected[n].shape)]
+             if n in present and not shape_fits(tuple(expected[n].shape), tuple(present[n]))]
     if not (missing or unexpected or wrong):
         return
     lines = [f"weights: {where} does not fit the model:"]

@@ -91,10 +91,11 @@ def random_tensors(expected: dict[str, Expected], seed: int, weight_std: float, 
     for name, e in expected.items():
         if e.optional:
             continue
+        shape = tuple(abs(int(n)) for n in e.shape)        # a size left to the tensor: its magnitude when made at random
         if e.role == "int":
-            yield name, torch.zeros(e.shape, dtype=torch.int32, device=device)
+            yield name, torch.zeros(shape, dtype=torch.int32, device=device)
             continue
-        yield name, random_tensor(seed, name, e.shape, norm_std if e.role == "vector" else weight_std, dtype, device)
+        yield name, random_tensor(seed, name, shape, norm_std if e.role == "vector" else weight_std, dtype, device)
 
 
 def write_model_folder(folder: str, config_dict: dict, expected: dict[str, Expected], seed: int,
