@@ -372,6 +372,7 @@ def experts_tc_ok(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, pai
     grouped kernel: bfloat16 on the device, enough rows per expert, sizes a TMA box takes."""
     E, F, W = w_up.shape
     return (x.is_cuda and x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0
+            and w_down.shape[2] % 8 == 0       # (gated experts: the second product's rows are half as wide as F)
             and x.stride(0) % 8 == 0 and pairs >= max(GROUP_ROWS_TC, EXPERTS_TC_ROWS * E))
 
 

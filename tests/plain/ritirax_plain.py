@@ -37,35 +37,49 @@ def distance_bucket(n: int, rows: int, far: float) -> int:
     return min(rows - 1, half + step)
 
 
+def biased_attention(q, k, v, scale, cap, rel, far, sink, first=0):
+    """q (Tq, H, d) at positions first, first + 1, ...; k (Tk, G, d), v (Tk, G, dv) at positions 0, 1, ...;
+    rel (rows, H) or None; sink (H,) or None.  Returns (Tq, H, dv)."""
+    Tq, H, _ = q.shape
+    Tk, G, _ = k.shape
+    i = torch.arange(Tq)[:, None] + first
+    j = torch.arange(Tk)[None, :]
+    seen = j <= i
+    which = None
+    if rel is not None:
+        rows = rel.shape[0]
+        which = torch.tensor([[distance_bucket(int(a) - b, rows, far) if b <= int(a) else 0 for b in range(Tk)]
+                              for a in i[:, 0]])
+    outs = []
+    for h in range(H):
+        g = h // (H // G)
+        s = (q[:, h] @ k[:, g].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        if which is not None:
+            s = s + rel[which, h]
+        s = s.masked_fill(~seen, float("-inf"))
+        top = s.max(dim=-1, keepdim=True).values
+        if sink is not None:
+            top = torch.maximum(top, sink[h])
+        e = torch.exp(s - top)
+        den = e.sum(dim=-1, keepdim=True)
+        if sink is not None:
+            den = den + torch.exp(sink[h] - top)
+        outs.append((e / den) @ v[:, g])
+    return torch.stack(outs, dim=1)
+
+
 def capped_attention(n, t, p, m, eps):
     """Grouped-query attention without a rotation: per-head RMS norm of q and k, a tanh cap on the scaled
     score, a learned bias by distance, every earlier key visible, and a sink in the softmax's denominator."""
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = n.shape[0]
-    q = (n @ t[p + "q"].T).view(T, H, d)
-    k = (n @ t[p + "k"].T).view(T, G, d)
+    q = unit_rms((n @ t[p + "q"].T).view(T, H, d), eps) * t[p + "q.norm"]
+    k = unit_rms((n @ t[p + "k"].T).view(T, G, d), eps) * t[p + "k.norm"]
     v = (n @ t[p + "v"].T).view(T, G, dv)
-    q = unit_rms(q, eps) * t[p + "q.norm"]
-    k = unit_rms(k, eps) * t[p + "k.norm"]
-    rel = t[p + "rel"]
-    rows = rel.shape[0]
-    cap = m.get("softcap") or 0.0
-    which = torch.tensor([[distance_bucket(i - j, rows, m["bias_max"]) if j <= i else 0 for j in range(T)]
-                          for i in range(T)])
-    seen = torch.tril(torch.ones(T, T, dtype=torch.bool))
-    outs = []
-    for h in range(H):
-        g = h // (H // G)
-        s = (q[:, h] @ k[:, g].T) * m["scale"]
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        s = s + rel[which, h]
-        s = s.masked_fill(~seen, float("-inf"))
-        top = torch.maximum(s.max(dim=-1, keepdim=True).values, t[p + "sink"][h])
-        e = torch.exp(s - top)
-        w = e / (e.sum(dim=-1, keepdim=True) + torch.exp(t[p + "sink"][h] - top))
-        outs.append(w @ v[:, g])
-    return torch.cat(outs, dim=-1) @ t[p + "o"].T
+    o = biased_attention(q, k, v, m["scale"], m.get("softcap") or 0.0, t[p + "rel"], m["bias_max"], t[p + "sink"])
+    return o.reshape(T, H * dv) @ t[p + "o"].T
 
 
 # --- rotation with stretched frequencies ------------------------------------------------------------------------
@@ -123,20 +137,28 @@ def latent_attention(n, t, p, m, eps):
     return o @ t[p + "o"].T
 
 
+def decay_recurrence(q, k, v, decay, S=None):
+    """q, k (T, H, d), v (T, H, dv), decay (H,): S <- decay S + k v^T, o = S^T q, token by token.
+    Returns (o (T, H, dv), the last S (H, d, dv))."""
+    T, H, d = q.shape
+    if S is None:
+        S = torch.zeros(H, d, v.shape[-1], dtype=q.dtype)
+    rows = []
+    for i in range(T):
+        S = decay[:, None, None] * S + k[i][:, :, None] * v[i][:, None, :]
+        rows.append(torch.einsum("hdv,hd->hv", S, q[i]))
+    return torch.stack(rows), S
+
+
 def lightning(n, t, p, m, eps):
-    """Linear attention with one fixed decay per head: S <- decay S + k v^T, o = S^T q, token by token."""
+    """Linear attention with one fixed decay per head, a norm over all heads' results together, a sigmoid gate."""
     H, d, dv = m["heads"], m["dim"], m["vdim"]
     T = n.shape[0]
     q = silu(n @ t[p + "q"].T).view(T, H, d)
     k = silu(n @ t[p + "k"].T).view(T, H, d)
     v = silu(n @ t[p + "v"].T).view(T, H, dv)
-    decay = torch.tensor(m["decay"], dtype=F64)
-    S = torch.zeros(H, d, dv, dtype=F64)
-    rows = []
-    for i in range(T):
-        S = decay[:, None, None] * S + k[i][:, :, None] * v[i][:, None, :]
-        rows.append(torch.einsum("hdv,hd->hv", S, q[i]).reshape(H * dv))
-    o = unit_rms(torch.stack(rows), eps) * t[p + "norm"]
+    o, _ = decay_recurrence(q, k, v, torch.tensor(m["decay"], dtype=F64))
+    o = unit_rms(o.reshape(T, H * dv), eps) * t[p + "norm"]
     return (o * torch.sigmoid(n @ t[p + "g"].T)) @ t[p + "o"].T
 
 
