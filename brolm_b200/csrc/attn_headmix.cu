@@ -3,6 +3,9 @@
 //
 // * query/key rows of hd and value rows of vd elements, each a multiple of 16 up to 256;
 // * a distance bias: slope[head] * (p - j) is taken off the scaled score of key j at query position p;
+// * a soft cap cap * tanh(score / cap) on the scaled score, a learned bias by distance after it (a table
+//   [query heads][dist_len] of which key j adds entry min(p - j, dist_len - 1)), and a sink, a number per query head
+//   whose exponential joins the softmax's denominator (prompt kernel and the first decode kernel);
 // * a window that keeps a sequence's first keys: key j is visible from p iff j <= p and
 //   (p - j < window or j < keep_first); in the paged cache the first `ring_from` places are held for good and
 //   the ring lies behind them;
@@ -39,6 +42,10 @@ struct HmArgs {
     float scale;
     int window, keep_first;
     const float* slopes;    // [n_kv * group] or null
+    float cap;              // > 0: cap * tanh(scaled score / cap)
+    const float* sink;      // [n_kv * group] or null
+    const float* dist_bias; // [n_kv * group][dist_len] or null
+    int dist_len;
     int sms;
     int n_splits;
     float* part_o;          // [B][n_q][n_vh][n_splits][vd]
@@ -46,6 +53,17 @@ struct HmArgs {
 };
 
 __device__ unsigned g_headmix_tickets[MAX_TICKETS];     // one per (sequence, block row); zero between launches
+
+// The score of key `dist` places back in log2 units: scale, cap, slope, the table's entry.  `masked` entries may
+// carry any distance; the clamp keeps the table's read in range.
+__device__ __forceinline__ float hm_score(float s, float scale, float cap, float inv_cap, float slope2, const float* db,
+                                          int dist_len, int dist) {
+    float v = s * scale;
+    if (cap > 0.0f) v = cap * fast_tanh(v * inv_cap);
+    v = v * LOG2E - slope2 * (float)dist;
+    if (db) v = fmaf(db[min(max(dist, 0), dist_len - 1)], LOG2E, v);
+    return v;
+}
 
 // ===========================================================================
 // prompts that start at position 0
@@ -120,13 +138,16 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
 
     int rpos[2];
     float slope2[2];           // slope in log2 units
+    const float* db[2];        // the head's row of the distance table
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = warp * 16 + (lane >> 2) + 8 * i;
         rpos[i] = r < rows_here ? (row0 + r) / a.group : -1;
-        slope2[i] = (a.slopes && r < rows_here) ? a.slopes[g * a.group + (row0 + r) % a.group] * LOG2E : 0.0f;
+        const int head = g * a.group + (r < rows_here ? (row0 + r) % a.group : 0);
+        slope2[i] = (a.slopes && r < rows_here) ? a.slopes[head] * LOG2E : 0.0f;
+        db[i] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
     }
-    const float scale2 = a.scale * LOG2E;
+    const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
     const uint32_t x = lane & 7;
     const uint32_t xhi_k = swz_k ? (x & 6u) << 4 : 0u, xhi_v = swz_v ? (x & 6u) << 4 : 0u;
@@ -170,7 +191,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
             for (int e = 0; e < 4; ++e) {
                 const int kp = tile_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
                 const int p = rpos[e >> 1];
-                float v = s[nt][e] * scale2 - slope2[e >> 1] * (float)(p - kp);
+                float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], db[e >> 1], a.dist_len, p - kp);
                 if (edge && !(p >= 0 && kp <= p && (p - kp < window || kp < keep))) v = -INFINITY;
                 s[nt][e] = v;
             }
@@ -238,6 +259,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
         const int rr = warp * 16 + (lane >> 2) + 8 * r;
         if (rr >= rows_here) continue;
         const int row = row0 + rr, tok = row / a.group, head = g * a.group + row % a.group;
+        if (a.sink && m[r] > -INFINITY) sum += fast_exp2(a.sink[head] * LOG2E - m[r]);
         const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
         const size_t at = (size_t)(q0 + tok) * a.out_stride + ((size_t)head * a.n_vh + c_out) * vd + (lane & 3) * 2;
 #pragma unroll
@@ -281,6 +303,7 @@ __device__ __forceinline__ void finish_decode(const HmArgs& a, float* stage0, in
         }
         const int head = g * a.group + row;
         if (a.n_splits == 1) {
+            if (a.sink && mx > -INFINITY) sum += fast_exp2(a.sink[head] * LOG2E - mx);
             const float res = sum > 0.0f ? acc / sum : 0.0f;
             const size_t at = (size_t)q_row * a.out_stride + ((size_t)head * n_vh + c_out) * vd + d;
             if (a.out_f32) ((float*)a.out)[at] = res;
@@ -329,6 +352,7 @@ __device__ __forceinline__ void finish_decode(const HmArgs& a, float* stage0, in
             sum += ml1.y * f;
         }
         sum = warp_sum(sum);
+        if (a.sink && mx > -INFINITY) sum += fast_exp2(a.sink[g * a.group + row] * LOG2E - mx);
         if (lane == 0) total[row] = sum;
     }
     __syncthreads();
@@ -456,12 +480,15 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_decode_kernel(HmArgs a)
     for (int i = 0; i < VD_MAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     float slope2[2];
+    const float* db[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + 8 * r;
-        slope2[r] = (a.slopes && row < a.group) ? a.slopes[g * a.group + row] * LOG2E : 0.0f;
+        const int head = g * a.group + (row < a.group ? row : 0);
+        slope2[r] = (a.slopes && row < a.group) ? a.slopes[head] * LOG2E : 0.0f;
+        db[r] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
     }
-    const float scale2 = a.scale * LOG2E;
+    const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES - 2>();
@@ -492,7 +519,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_decode_kernel(HmArgs a)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kp = kbase + nt * 8 + (e & 1);
-                const float v = s[nt][e] * scale2 - slope2[e >> 1] * (float)(pos - kp);
+                const float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], db[e >> 1], a.dist_len, pos - kp);
                 s[nt][e] = (kp <= pos && (kp >= key_lo || kp < keep)) ? v : -INFINITY;
             }
         }
@@ -867,8 +894,8 @@ int check_hm(int hd, int vd, int group, int n_kv, int q_stride, int out_stride, 
 BROLM_API int brolm_attn_headmix_prefill(const void* q, int q_stride, void* out, int out_stride, int out_f32,
                                          const void* cu_q, const void* k, int kv_stride, const void* v, int v_stride,
                                          int n_kv, int group, int hd, int vd, float scale, int window, int keep_first,
-                                         const void* slopes, int all_values, int batch, int max_q_len,
-                                         cudaStream_t stream) {
+                                         const void* slopes, int all_values, int batch, int max_q_len, float cap,
+                                         const void* sink, const void* dist_bias, int dist_len, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     int st = check_hm(hd, vd, group, n_kv, q_stride, out_stride, batch, all_values);
     if (st) return st;
@@ -879,6 +906,9 @@ BROLM_API int brolm_attn_headmix_prefill(const void* q, int q_stride, void* out,
     a.cu_q = (const int32_t*)cu_q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.kv_stride = kv_stride; a.v_stride = v_stride;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.vd = vd; a.n_vh = all_values ? n_kv : 1;
     a.scale = scale; a.window = window; a.keep_first = keep_first; a.slopes = (const float*)slopes;
+    if ((cap > 0.0f || sink || dist_bias) && all_values) return BROLM_ERR_BAD_SIZE;
+    if (dist_bias && dist_len <= 0) return BROLM_ERR_BAD_SIZE;
+    a.cap = cap; a.sink = (const float*)sink; a.dist_bias = (const float*)dist_bias; a.dist_len = dist_len;
     a.sms = device_sm_count(); a.n_splits = 1;
     return by_size(hd, vd,
                    [&] { return launch_hm_prefill<128, 64>(a, batch, max_q_len, stream); },
@@ -898,7 +928,8 @@ BROLM_API int brolm_attn_headmix_decode(const void* q, int q_stride, void* out, 
                                         const void* page_table, int pt_stride, int ring, int ring_from, int page_size,
                                         int n_kv, int group, int hd, int vd, float scale, int window, int keep_first,
                                         const void* slopes, int all_values, int batch, int n_splits, void* part_o,
-                                        void* part_ml, cudaStream_t stream) {
+                                        void* part_ml, float cap, const void* sink, const void* dist_bias, int dist_len,
+                                        cudaStream_t stream) {
     if (batch <= 0) return BROLM_OK;
     int st = check_hm(hd, vd, group, n_kv, q_stride, out_stride, batch, all_values);
     if (st) return st;
@@ -916,6 +947,9 @@ BROLM_API int brolm_attn_headmix_decode(const void* q, int q_stride, void* out, 
     a.pt_stride = pt_stride; a.ring = ring; a.ring_from = ring_from;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.vd = vd; a.n_vh = all_values ? n_kv : 1;
     a.scale = scale; a.window = window; a.keep_first = keep_first; a.slopes = (const float*)slopes;
+    if ((cap > 0.0f || sink || dist_bias) && all_values) return BROLM_ERR_BAD_SIZE;
+    if (dist_bias && dist_len <= 0) return BROLM_ERR_BAD_SIZE;
+    a.cap = cap; a.sink = (const float*)sink; a.dist_bias = (const float*)dist_bias; a.dist_len = dist_len;
     a.sms = device_sm_count(); a.n_splits = n_splits; a.part_o = (float*)part_o; a.part_ml = (float*)part_ml;
     if (all_values && n_kv > 1) {
         if (const size_t smem = decode_all_smem(hd, vd, n_kv, group, n_splits)) {

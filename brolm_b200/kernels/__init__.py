@@ -1280,22 +1280,27 @@ def headmix_splits(batch: int, blocks_y: int, max_kv_len: int, window: int, keep
 def attention_headmix_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                               n_kv: int, group: int, head_dim: int, v_dim: int, scale: float, window: int, batch: int,
                               max_q_len: int, slopes: Optional[torch.Tensor] = None, keep_first: int = 0,
-                              all_values: bool = False) -> None:
+                              all_values: bool = False, cap: float = 0.0, sink: Optional[torch.Tensor] = None,
+                              dist_bias: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention (bfloat16 operands) of whole prompts that start at position 0, with value rows of
     their own size, distance slopes and a window that keeps first keys.  ``out`` is bfloat16 or float32,
     (tokens, heads * v_dim); with ``all_values`` every head's weights meet the values of every kv head and
-    ``out`` is (tokens, heads * n_kv * v_dim), head h's row being [n_kv][v_dim]."""
+    ``out`` is (tokens, heads * n_kv * v_dim), head h's row being [n_kv][v_dim].  ``cap``, ``sink`` and
+    ``dist_bias`` as in ``attention_simt`` (not together with ``all_values``)."""
     _check_sink(slopes, n_kv * group)
+    _check_sink(sink, n_kv * group)
+    _check_dist_bias(dist_bias, n_kv * group)
     assert q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
     assert out.dtype in (torch.bfloat16, torch.float32)
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert out.shape[-1] >= n_kv * group * v_dim * (n_kv if all_values else 1) and cu_q.dtype == torch.int32
     f = _fn("attn_headmix", "brolm_attn_headmix_prefill",
             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+             c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(cu_q),
              _ptr(k), k.stride(0), _ptr(v), v.stride(0), n_kv, group, head_dim, v_dim, scale, int(window),
-             int(keep_first), _ptr(slopes), 1 if all_values else 0, batch, max_q_len, _stream()),
+             int(keep_first), _ptr(slopes), 1 if all_values else 0, batch, max_q_len, float(cap), _ptr(sink),
+             _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _stream()),
            "attention_headmix_prefill")
 
 
@@ -1304,11 +1309,14 @@ def attention_headmix_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Ten
                              ring_from: int, page_size: int, n_kv: int, group: int, head_dim: int, v_dim: int,
                              scale: float, window: int, batch: int, n_splits: int,
                              slopes: Optional[torch.Tensor] = None, keep_first: int = 0,
-                             all_values: bool = False) -> None:
+                             all_values: bool = False, cap: float = 0.0, sink: Optional[torch.Tensor] = None,
+                             dist_bias: Optional[torch.Tensor] = None) -> None:
     """The same attention for one new token per sequence over the paged cache (pages of 64 keys, at most 16
     query heads per kv head).  The splits' partial results go through float32 scratch made here; the block
     that finishes last among them merges them."""
     _check_sink(slopes, n_kv * group)
+    _check_sink(sink, n_kv * group)
+    _check_dist_bias(dist_bias, n_kv * group)
     assert q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16
     assert out.dtype in (torch.bfloat16, torch.float32) and q.stride(-1) == 1 and out.stride(-1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -1325,11 +1333,12 @@ def attention_headmix_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Ten
     f = _fn("attn_headmix", "brolm_attn_headmix_decode",
             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
-             c_void_p, c_void_p])
+             c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(cu_q),
              _ptr(kv_len), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.stride(0), ring, int(ring_from),
              page_size, n_kv, group, head_dim, v_dim, scale, int(window), int(keep_first), _ptr(slopes),
-             1 if all_values else 0, batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()),
+             1 if all_values else 0, batch, n_splits, _ptr(part_o), _ptr(part_ml), float(cap), _ptr(sink), _ptr(dist_bias),
+             dist_bias.shape[1] if dist_bias is not None else 0, _stream()),
            "attention_headmix_decode")
 
 

@@ -367,7 +367,7 @@ class Attention(Part):
                 source = dict(k_pages=k_pages, v_pages=v_pages, page_table=table, ring=ring, page_size=page,
                               ring_from=ctx.ring_from(kv_entry))
             # bfloat16 without a chunked mask runs on the tensor cores, all else on the exact kernel
-            tensor = self._tensor_cores(ctx) and not self.chunk and not scored and \
+            tensor = self._tensor_cores(ctx) and not self.chunk and not (scored and self.talk) and \
                 kernels.attention_headmix_ok(self.head_dim, self.v_dim, group, ctx.mode != "prefill", page)
 
             def attend(dst, all_values=False):
@@ -379,7 +379,7 @@ class Attention(Part):
                     return
                 args = dict(n_kv=self.n_kv, group=group, head_dim=self.head_dim, v_dim=self.v_dim, scale=self.scale,
                             window=self.window or 0, batch=ctx.batch, slopes=self.slopes, keep_first=self.keep_first,
-                            all_values=all_values)
+                            all_values=all_values, cap=self.softcap, sink=self.sink, dist_bias=self.dist_bias)
                 if ctx.mode == "prefill":
                     kernels.attention_headmix_prefill(q, dst, ctx.cu_q, k, v, max_q_len=ctx.max_q_len, **args)
                 else:

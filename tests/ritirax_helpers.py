@@ -55,25 +55,26 @@ CFG_S = dict(
             latent(2, 8, 8, 16, 24, 0.3, 100.0, scaling=(2.0, 32, 8.0, 1.0), mlp=moe(24, 4, 4, scale=0.7, groups=(2, 2))),
             lightning(3, 8, 16, (0.5, 0.9, 0.99))])
 
-# T: real routing (3 of 6 in 2 of 3 groups; 1 of 4 without groups, scale or shared expert), as many key heads as
+# T: real routing (3 of 6 in 2 of 3 groups; 1 of 4 in groups of one expert that all stay open, no scale, no shared
+# expert), as many key heads as
 # query heads, head sizes that are no multiples of 8 or of 4, no soft cap, a table with an odd number of rows, a rotated
 # part smaller than the unrotated one and no stretching, one lightning head, sizes that are no multiples of 16.
 CFG_T = dict(
     architecture="Ritirax", vocab=50, width=40, norm=dict(eps=1e-6), embedding=dict(scale=0.5),
     layers=[attention(3, 3, 12, 20, 0.25, 0.0, 25, 7, mlp=moe(20, 6, 3, scale=2.0, groups=(3, 2), shared=12)),
-            lightning(1, 6, 12, (0.97,), mlp=moe(36, 4, 1)),
+            lightning(1, 6, 12, (0.97,), mlp=moe(36, 4, 1, groups=(4, 4))),
             latent(3, 12, 4, 8, 20, 0.2, 10000.0, mlp=dense(56)),
             attention(6, 1, 8, 8, 0.35, 5.0, 300, 12, mlp=dense(24))])
 
 # U: distances far into the logarithmic rows and beyond the last (a table of 32 rows that ends at 200, prompts of 300),
 # positions far beyond the stretch's original length, key and value heads of one size that is a multiple of 16, a decay
-# of exactly 1 and one of 0.999 over hundreds of tokens, a router whose groups all stay open but whose top is below the
-# experts, a group of one expert each.
+# of exactly 1 and one of 0.999 over hundreds of tokens; every routed layer uses all of its experts, so that a rounded
+# run can be held against the oracle here too.
 CFG_U = dict(
     architecture="Ritirax", vocab=64, width=32, norm=dict(eps=1e-5), embedding=dict(scale=5.5),
-    layers=[latent(4, 16, 16, 16, 32, 0.18, 1000.0, scaling=(8.0, 64, 16.0, 2.0), mlp=moe(16, 4, 2, scale=1.0, groups=(4, 3))),
+    layers=[latent(4, 16, 16, 16, 32, 0.18, 1000.0, scaling=(8.0, 64, 16.0, 2.0), mlp=moe(16, 4, 4, scale=1.0, groups=(2, 2))),
             attention(4, 1, 32, 32, 0.18, 30.0, 200, 32, mlp=dense(24)),
-            lightning(2, 32, 64, (0.999, 1.0), mlp=moe(16, 2, 1, scale=3.0, shared=24)),
+            lightning(2, 32, 64, (0.999, 1.0), mlp=moe(16, 2, 2, scale=3.0, shared=24)),
             attention(2, 2, 16, 48, 0.25, 0.0, 9, 4)])
 
 CONFIGS = {"S": (CFG_S, 3, 0.15), "T": (CFG_T, 4, 0.2), "U": (CFG_U, 5, 0.2)}      # name -> (config, seed, weight std)

@@ -75,6 +75,13 @@ def test_a_key_that_carries_the_weight_at_every_step_of_the_table(dtype, H, G, h
                            window=0, batch=1, max_q_len=T, k=k.reshape(T, -1).to(DEV), v=v.reshape(T, -1).to(DEV), v_dim=vd,
                            sink=sink.to(DEV))
     assert float((out.view(T, H, vd).double().cpu() - ref).abs().max()) > 0.05
+    if dtype == torch.bfloat16 and kernels.attention_headmix_ok(hd, vd, H // G, False):
+        # the same on the tensor cores
+        out.zero_()
+        kernels.attention_headmix_prefill(q.reshape(T, -1).to(DEV), out, cu, k.reshape(T, -1).to(DEV), v.reshape(T, -1).to(DEV),
+                                          n_kv=G, group=H // G, head_dim=hd, v_dim=vd, scale=1.0, window=0, batch=1,
+                                          max_q_len=T, cap=cap, sink=sink.to(DEV), dist_bias=dist_table(rel, far).to(DEV))
+        close(out.view(T, H, vd), ref, dtype, "packed, tensor cores")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -82,7 +89,7 @@ def test_far_keys_from_scattered_pages(dtype):
     """Decoding: one query per sequence over pages in a scattered order with NaN in the places never written; the key
     that carries the weight lies at a page's last place, at the next page's first, and far beyond the table's end."""
     g = torch.Generator().manual_seed(7)
-    H, G, hd, vd, rows, far, page = 4, 2, 16, 24, 8, 40.0, 64
+    H, G, hd, vd, rows, far, page = 4, 2, 16, 48, 8, 40.0, 64
     lengths = [1, 64, 65, 130, 400, 41]
     targets = [0, 63, 64, 63, 5, 1]                                   # position of the key each sequence's query looks for
     rel = 3.0 * torch.randn(rows, H, generator=g)
@@ -114,10 +121,22 @@ def test_far_keys_from_scattered_pages(dtype):
                            page_table=pt.to(DEV), ring=1 << 30, page_size=page, v_dim=vd, sink=sink.to(DEV),
                            dist_bias=dist_table(rel, far).to(DEV))
     assert bool(torch.isfinite(out.float()).all()), "a place of the cache that was never written was read"
+    refs = [plain.biased_attention(qs[b].double()[None], ks[b].double(), vs[b].double(), 1.0, 15.0, rel.double(), far,
+                                   sink.double(), first=n - 1)[0] for b, n in enumerate(lengths)]
     for b, n in enumerate(lengths):
-        ref = plain.biased_attention(qs[b].double()[None], ks[b].double(), vs[b].double(), 1.0, 15.0, rel.double(), far,
-                                     sink.double(), first=n - 1)[0]
-        close(out[b].view(H, vd), ref, dtype, f"sequence of {n}")
+        close(out[b].view(H, vd), refs[b], dtype, f"sequence of {n}")
+    if dtype == torch.bfloat16:
+        # the same on the tensor cores, the keys of a sequence in one piece and cut into three and seven
+        for splits in (1, 3, 7):
+            out.zero_()
+            kernels.attention_headmix_decode(torch.stack(qs).reshape(B, -1).to(DEV), out,
+                                             torch.arange(B + 1, dtype=torch.int32, device=DEV),
+                                             torch.tensor(lengths, dtype=torch.int32, device=DEV), kp.to(DEV), vp.to(DEV),
+                                             pt.to(DEV), ring=1 << 30, ring_from=0, page_size=page, n_kv=G, group=H // G,
+                                             head_dim=hd, v_dim=vd, scale=1.0, window=0, batch=B, n_splits=splits, cap=15.0,
+                                             sink=sink.to(DEV), dist_bias=dist_table(rel, far).to(DEV))
+            for b, n in enumerate(lengths):
+                close(out[b].view(H, vd), refs[b], dtype, f"sequence of {n}, tensor cores, {splits} splits")
 
 
 def test_a_sink_that_swallows_a_head():
