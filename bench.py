@@ -25,6 +25,11 @@ main kernels' fractions of their rooflines.  One JSON line of its own shape; the
 ``--arch neburax [--size s|m]``: the same for the Neburax design (state-space layers, chunked attention beside a
 gated recurrence, routed experts with a shared expert), beside Gemma 2 at equal sizes.
 
+``--arch ritirax [--size s|m]``: the Ritirax design (linear attention with a fixed decay per head, capped attention with
+a distance bias and a sink, gated latent attention, routed experts chosen among groups with a gated shared expert) beside
+the closest design the library has, Neburax (state-space layers, attention beside a recurrence, routed experts with a
+shared expert), built to the same width, heads, experts and layer count.
+
 More than one GPU is not what this library does: ``--gpus N`` with N > 1 says
 so and exits with 2.
 """
@@ -550,6 +555,121 @@ def kedasun_main(args, pk) -> int:
     return 0
 
 
+# --arch ritirax: a lightning layer with a dense feed-forward, a capped attention layer, a latent attention layer and a
+# second lightning layer, the last three with routed experts (the sizes of the Neburax run of the same letter)
+RITIRAX_SIZES = {
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, lat_dim=64, lat_rot=64, lat_vdim=64, kv_rank=192,
+              experts=32, groups=8, keep=4, top=4, ff=1024, shared=1024, dense_ff=4096, vocab=32768),
+    "m": dict(width=3072, heads=24, kv_heads=4, dim=128, vdim=128, lat_dim=128, lat_rot=64, lat_vdim=128, kv_rank=192,
+              experts=64, groups=8, keep=4, top=6, ff=1024, shared=2048, dense_ff=6144, vocab=65536),
+}
+
+
+def ritirax_main(args, pk) -> int:
+    import torch
+
+    import brolm_b200 as bb
+
+    name = args.size if args.size in RITIRAX_SIZES else "s"
+    z, nz = RITIRAX_SIZES[name], NEBURAX_SIZES[name]
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    W, H, G, d, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    moe = dict(kind="moe", expert=dict(ff=z["ff"]), shared=dict(ff=z["shared"]),
+               router=dict(experts=z["experts"], top=z["top"], scale=2.5, groups=dict(count=z["groups"], keep=z["keep"])))
+    decay = [1.0 - 2.0 ** (-3.0 - 7.0 * h / max(H - 1, 1)) for h in range(H)]
+    light = dict(heads=H, dim=d, vdim=dv, decay=decay)
+    attn = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, softcap=30.0, bias_max=128, bias_rows=32)
+    lat = dict(heads=H, dim=z["lat_dim"], rot_dim=z["lat_rot"], vdim=z["lat_vdim"], kv_rank=z["kv_rank"],
+               scale=(z["lat_dim"] + z["lat_rot"]) ** -0.5,
+               rot=dict(base=10000.0, dims=z["lat_rot"], scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0)))
+    layers = [dict(type="lightning", mixer=light, mlp=dict(kind="dense", ff=z["dense_ff"])),
+              dict(type="attention", mixer=attn, mlp=moe), dict(type="latent_attention", mixer=lat, mlp=moe),
+              dict(type="lightning", mixer=light, mlp=moe)]
+    rcfg = bb.RitiraxConfig.from_dict(dict(architecture="Ritirax", vocab=z["vocab"], width=W, layers=layers,
+                                           norm=dict(eps=1e-5), embedding=dict(scale=W ** 0.5)))
+    # the closest design at the same sizes: the Neburax run of the same letter
+    nmoe = dict(kind="moe", expert=dict(ff=nz["ff"]), router=dict(experts=nz["experts"], top=nz["top"], identity=nz["identity"]),
+                shared=dict(ff=nz["shared"]))
+    ssm = dict(heads=nz["ssm_heads"], vdim=nz["ssm_vdim"], state=nz["state"], groups=nz["groups"], norm_groups=nz["groups"], conv=4)
+    pair = dict(left=dict(heads=nz["heads"], kv_heads=nz["kv_heads"], dim=nz["dim"], vdim=nz["vdim"], scale=nz["dim"] ** -0.5,
+                          mask=dict(size=4096)),
+                right=dict(width=nz["rec_width"], blocks=nz["rec_blocks"], conv=4), left_scale=1.0, right_scale=1.0)
+    nlayers = [dict(type="mamba2", mixer=ssm, mlp=dict(kind="dense", ff=nz["dense_ff"])),
+               dict(type="parallel", mixer=pair, mlp=nmoe), dict(type="mamba2", mixer=ssm, mlp=nmoe),
+               dict(type="parallel", mixer=pair, mlp=nmoe, weights_of=1)]
+    ncfg = bb.NeburaxConfig.from_dict(dict(architecture="Neburax", vocab=nz["vocab"], width=W, layers=nlayers,
+                                           norm=dict(eps=1e-5)))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps, warmup, batch, context, prompt_len = args.steps or 64, max(args.warmup, 3), args.batch or 8, 1280, 2048
+    common = (dev, flush, steps, warmup, batch, context, prompt_len)
+    r, nb = measure_design(rcfg, z["vocab"], *common), measure_design(ncfg, z["vocab"], *common)
+    T, top, ff = prompt_len, z["top"], z["ff"]
+    keys = T * (T + 1) // 2                                                    # visible (query, key) pairs of a prompt
+    row = (z["kv_rank"] + z["lat_rot"] + 15) // 16 * 16                        # the cached row of the latent layer
+    nh, P, N, grp = nz["ssm_heads"], nz["ssm_vdim"], nz["state"], nz["groups"]
+    inner, cols = nh * P, nh * P + 2 * grp * N
+    tf, gb = pk["bf16_burst"] * 1e12, pk["hbm_gbs"] * 1e9
+    active = z["experts"] * (1.0 - (1.0 - top / z["experts"]) ** batch)
+    nactive = nz["experts"] * (1.0 - (1.0 - nz["top"] / (nz["experts"] + nz["identity"])) ** batch)
+    # (kernel-name fragment, work of all its launches in one pass over the layers, bound)
+    rows = [
+        ("ritirax prefill", r["prefill_kernels"], [
+            ("grouped_tc_kernel", 3 * 2.0 * T * top * ff * W * 3, "flops"),
+            ("attn_headmix_prefill", 2.0 * H * (d + dv) * keys, "flops"),
+            ("attn_prefill_mma", 2.0 * H * 2 * row * keys, "flops"),
+            ("decay_scan", 2 * T * (H * (2 * d + dv) + H * dv) * 4.0, "bytes"),
+        ]),
+        ("closest prefill", nb["prefill_kernels"], [
+            ("grouped_tc_kernel", 3 * 2.0 * T * nz["top"] * nz["ff"] * W * 3, "flops"),
+            ("attn_prefill", 2 * 2.0 * nz["heads"] * (nz["dim"] + nz["vdim"]) * keys, "flops"),
+            ("ssm_", 2 * T * (cols + inner + nh) * 4.0, "bytes"),
+            ("gated_scan", 2 * T * nz["rec_width"] * (4 * 4.0 + 2), "bytes"),
+        ]),
+        ("ritirax decode", r["decode_kernels"], [
+            ("fast_kernel<64, 64, 4, false>", 3 * active * ff * W * 2.0 * 3, "bytes"),
+            ("attn_headmix_decode", batch * context * G * (d + dv) * 2.0, "bytes"),
+            ("attn_decode_mma", batch * context * row * 2.0, "bytes"),
+            ("decay_scan", 2 * batch * H * d * dv * 4.0 * 2, "bytes"),
+        ]),
+        ("closest decode", nb["decode_kernels"], [
+            ("fast_kernel<64, 64, 4, false>", 3 * nactive * nz["ff"] * W * 2.0 * 3, "bytes"),
+            ("attn_decode", 2 * batch * context * nz["kv_heads"] * (nz["dim"] + nz["vdim"]) * 2.0, "bytes"),
+            ("ssm_", 2 * batch * nh * P * N * 4.0 * 2, "bytes"),
+        ]),
+    ]
+    table = []
+    for title, kern, wanted in rows:
+        for frag, work, bound in wanted:
+            us = sum(v["us"] for k, v in kern.items() if frag in k)
+            n = sum(v["n"] for k, v in kern.items() if frag in k)
+            if not n:
+                continue
+            frac = work / (us * 1e-6) / (tf if bound == "flops" else gb)
+            table.append({"step": title, "kernel": frag, "launches": n, "us": round(us, 2),
+                          "bound": "tensor" if bound == "flops" else "hbm", "frac_of_measured_peak": round(frac, 4)})
+    result = {
+        "metric": f"Ritirax decode tokens/s (size {name}, batch {batch}, context {context}) beside Neburax at equal sizes",
+        "value": round(batch * 1000.0 / r["decode_ms"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(r["decode_ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "brolm_b200", "clocks": r["clocks"], "gpu_launches": r["launches"],
+        "config": {"model": "Ritirax", **{k: v for k, v in z.items()}, "layers": len(layers), "global_batch": batch,
+                   "seq_len": context, "closest": {"model": "Neburax", **{k: v for k, v in nz.items()}},
+                   "l2": "the prompt is timed after an L2 flush; a decode step reads more than the L2 holds",
+                   "peaks": pk["source"]},
+        "ritirax": {"prefill_tok_s": round(T * 1000.0 / r["prefill_ms"], 1), "prefill_ms": round(r["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / r["decode_ms"], 1), "decode_ms": round(r["decode_ms"], 4)},
+        "closest": {"prefill_tok_s": round(T * 1000.0 / nb["prefill_ms"], 1), "prefill_ms": round(nb["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / nb["decode_ms"], 1), "decode_ms": round(nb["decode_ms"], 4)},
+        "kernels": table,
+        "by_kernel_us": {"ritirax_prefill": _top(r["prefill_kernels"], 28), "closest_prefill": _top(nb["prefill_kernels"], 24),
+                         "ritirax_decode": _top(r["decode_kernels"], 28), "closest_decode": _top(nb["decode_kernels"], 24)},
+    }
+    print(json.dumps(result))
+    return 0
+
+
 def _by_kernel(events) -> dict:
     """Device records -> {kernel name: {"us": total time, "n": launches}}."""
     out: dict = {}
@@ -568,8 +688,9 @@ def _top(kern: dict, n: int = 14) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik", "neburax", "kedasun"],
-                    help="banevik, neburax, kedasun: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m)")
+    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik", "neburax", "kedasun", "ritirax"],
+                    help="banevik, neburax, kedasun: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m); "
+                         "ritirax: beside Neburax at equal sizes")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=0, help="decode steps in a timed region (default 64; 128 for 9b)")
     ap.add_argument("--warmup", type=int, default=8)
@@ -597,6 +718,8 @@ def main() -> int:
         return neburax_main(args, peaks())
     if args.arch == "kedasun":
         return kedasun_main(args, peaks())
+    if args.arch == "ritirax":
+        return ritirax_main(args, peaks())
     if args.size not in SIZES:
         print(f"bench.py: --size {args.size} goes with --arch banevik, neburax or kedasun")
         return 2

@@ -139,6 +139,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
     int rpos[2];
     float slope2[2];           // slope in log2 units
     const float* db[2];        // the head's row of the distance table
+    float db_far[2];           // its last entry, in log2 units: what every key of a tile far enough back adds
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = warp * 16 + (lane >> 2) + 8 * i;
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
         const int head = g * a.group + (r < rows_here ? (row0 + r) % a.group : 0);
         slope2[i] = (a.slopes && r < rows_here) ? a.slopes[head] * LOG2E : 0.0f;
         db[i] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
+        db_far[i] = a.dist_bias ? db[i][a.dist_len - 1] * LOG2E : 0.0f;
     }
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
@@ -185,13 +187,16 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
         // scale, distance bias, mask
         const int tile_lo = t * KT, tile_hi = tile_lo + KT - 1;
         const bool edge = tile_hi > tok_lo || tile_lo < tok_hi - window + 1;
+        const bool far_tile = a.dist_bias && tok_lo - tile_hi >= a.dist_len - 1;     // no read of the table in this tile
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kp = tile_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
                 const int p = rpos[e >> 1];
-                float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], db[e >> 1], a.dist_len, p - kp);
+                float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], far_tile ? nullptr : db[e >> 1],
+                                   a.dist_len, p - kp);
+                if (far_tile) v += db_far[e >> 1];
                 if (edge && !(p >= 0 && kp <= p && (p - kp < window || kp < keep))) v = -INFINITY;
                 s[nt][e] = v;
             }
@@ -479,7 +484,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_decode_kernel(HmArgs a)
 #pragma unroll
     for (int i = 0; i < VD_MAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float slope2[2];
+    float slope2[2], db_far[2];
     const float* db[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -487,6 +492,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_decode_kernel(HmArgs a)
         const int head = g * a.group + (row < a.group ? row : 0);
         slope2[r] = (a.slopes && row < a.group) ? a.slopes[head] * LOG2E : 0.0f;
         db[r] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
+        db_far[r] = a.dist_bias ? db[r][a.dist_len - 1] * LOG2E : 0.0f;
     }
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
@@ -514,12 +520,15 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_decode_kernel(HmArgs a)
             }
         }
         const int kbase = t * KT + warp * 16 + (lane & 3) * 2;
+        const bool far_tile = a.dist_bias && pos - (t * KT + KT - 1) >= a.dist_len - 1;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kp = kbase + nt * 8 + (e & 1);
-                const float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], db[e >> 1], a.dist_len, pos - kp);
+                float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], far_tile ? nullptr : db[e >> 1],
+                                   a.dist_len, pos - kp);
+                if (far_tile) v += db_far[e >> 1];
                 s[nt][e] = (kp <= pos && (kp >= key_lo || kp < keep)) ? v : -INFINITY;
             }
         }

@@ -14,8 +14,12 @@
 // decay_scan_kernel: a block of 128 threads takes one (sequence, head) and 128 / DS value columns; the DS lanes of a
 // column keep NJ float4 of the column's states each (d = 4 (j DS + ds) + e), so that q and k are read as float4 from
 // shared memory and a column's state row is read and written in contiguous runs.  Tokens are staged sixteen at a
-// time.  The sum over d of a column is folded across its DS lanes by shuffles.  Sequential in the tokens: the
-// order of the additions of a token's result does not depend on how the sequence was cut into steps.
+// time (float rows by cp.async through two buffers).  The sum over d of a column is four sums side by side in a lane,
+// then folded across its DS lanes by shuffles, sixteen tokens at once.  Sequential in the tokens: the order of the
+// additions of a token's result does not depend on how the sequence was cut into steps, only (through DS) on the
+// launch's size.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -35,6 +39,8 @@ struct ScanArgs {
     float* out;               // [tokens][ldo] float; head h at h * dv
     long ldo;
     int ds;                   // lanes per value column (a power of two, at most 32)
+    int vec;                  // float rows: every run of q, k and v starts at a multiple of 16 bytes
+    int early;                // a step of single tokens: takes part in programmatic launch
 };
 
 constexpr int SCAN_TC = 16;
@@ -45,15 +51,27 @@ __device__ __forceinline__ float read_act(const X* p, int act) {
     return act == 1 ? v / (1.0f + expf(-v)) : v;
 }
 
-template <typename X, int NJ>
+__device__ __forceinline__ void scan_cp4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void scan_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// Float rows are staged through two buffers filled by cp.async, the next sixteen tokens on their way while these are
+// worked on, and the activation is applied in place once a buffer has landed; bfloat16 rows are converted as they
+// are read, one buffer.
+// DSC > 0: the lanes per column are known to the compiler and NJ * DSC float4 are exactly a row of d (no padding, no
+// bounds in the inner loop, every offset a constant); DSC = 0: any d, lanes per column from the launch.
+template <typename X, int NJ, int DSC>
 __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float sm[];
-    pdl_trigger();
-    const int DS = a.ds, VT = 128 / DS;
-    const int dp = a.dp, dp4 = dp >> 2;
-    float* sq = sm;                       // [TC][dp]
-    float* sk = sq + SCAN_TC * dp;        // [TC][dp]
-    float* sv = sk + SCAN_TC * dp;        // [TC][VT]
+    if (a.early) pdl_trigger();
+    constexpr bool ASYNC = sizeof(X) == 4;
+    constexpr bool EXACT = DSC > 0;
+    const int DS = EXACT ? DSC : a.ds, VT = 128 / DS;
+    const int dp = EXACT ? 4 * NJ * DSC : a.dp, dp4 = dp >> 2;
+    const int stage = SCAN_TC * (2 * dp + VT);        // q [TC][dp], k [TC][dp], v [TC][VT]
     const int b = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * VT;
     const int kv_len = a.kv_len[b];
     if (kv_len <= 0) return;
@@ -71,46 +89,160 @@ __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
         if (live && f < dp4) s4 = *reinterpret_cast<const float4*>(st + 4 * f);
         S[4 * j] = s4.x; S[4 * j + 1] = s4.y; S[4 * j + 2] = s4.z; S[4 * j + 3] = s4.w;
     }
+    if (ASYNC) {
+        // the padding of d to a multiple of four, and value columns beyond dv, stay zero in both buffers
+        for (int i = threadIdx.x; i < 2 * stage; i += 128) sm[i] = 0.0f;
+        __syncthreads();
+    }
     pdl_wait();
     const X* base = (const X*)a.qkv;
-    for (int t0 = 0; t0 < q_len; t0 += SCAN_TC) {
-        const int n_tok = min(SCAN_TC, q_len - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < n_tok * dp; idx += 128) {
-            const int tt = idx / dp, c = idx - tt * dp;
-            const X* row = base + (size_t)(q0 + t0 + tt) * a.ld;
-            sq[idx] = c < a.d ? read_act(row + a.q_off + h * a.d + c, a.act) : 0.0f;
-            sk[idx] = c < a.d ? read_act(row + a.k_off + h * a.d + c, a.act) : 0.0f;
+    const int n_chunks = (q_len + SCAN_TC - 1) / SCAN_TC;
+    const int vt_here = min(VT, a.dv - v0);
+
+    auto issue = [&](int chunk) {                      // float rows only
+        float* sq = sm + (chunk & 1) * stage;
+        float* sk = sq + SCAN_TC * dp;
+        float* sv = sk + SCAN_TC * dp;
+        const int t0 = chunk * SCAN_TC, n_tok = min(SCAN_TC, q_len - t0);
+        const float* fb = reinterpret_cast<const float*>(base);
+        if (a.vec) {
+            const int d4 = a.d >> 2, v4 = vt_here >> 2;
+            for (int idx = threadIdx.x; idx < n_tok * d4; idx += 128) {
+                const int tt = idx / d4, c = (idx - tt * d4) << 2;
+                const float* row = fb + (size_t)(q0 + t0 + tt) * a.ld + h * a.d + c;
+                scan_cp16(sq + tt * dp + c, row + a.q_off);
+                scan_cp16(sk + tt * dp + c, row + a.k_off);
+            }
+            for (int idx = threadIdx.x; idx < n_tok * v4; idx += 128) {
+                const int tt = idx / v4, c = (idx - tt * v4) << 2;
+                scan_cp16(sv + tt * VT + c, fb + (size_t)(q0 + t0 + tt) * a.ld + a.v_off + h * a.dv + v0 + c);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < n_tok * a.d; idx += 128) {
+                const int tt = idx / a.d, c = idx - tt * a.d;
+                const float* row = fb + (size_t)(q0 + t0 + tt) * a.ld + h * a.d + c;
+                scan_cp4(sq + tt * dp + c, row + a.q_off);
+                scan_cp4(sk + tt * dp + c, row + a.k_off);
+            }
+            for (int idx = threadIdx.x; idx < n_tok * vt_here; idx += 128) {
+                const int tt = idx / vt_here, c = idx - tt * vt_here;
+                scan_cp4(sv + tt * VT + c, fb + (size_t)(q0 + t0 + tt) * a.ld + a.v_off + h * a.dv + v0 + c);
+            }
         }
-        for (int idx = threadIdx.x; idx < n_tok * VT; idx += 128) {
-            const int tt = idx / VT, c = idx - tt * VT;
-            const X* row = base + (size_t)(q0 + t0 + tt) * a.ld;
-            sv[idx] = v0 + c < a.dv ? read_act(row + a.v_off + h * a.dv + v0 + c, a.act) : 0.0f;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    if (ASYNC) issue(0);
+    for (int kc = 0; kc < n_chunks; ++kc) {
+        const int t0 = kc * SCAN_TC, n_tok = min(SCAN_TC, q_len - t0);
+        float* sq = sm + (ASYNC ? (kc & 1) * stage : 0);
+        float* sk = sq + SCAN_TC * dp;
+        float* sv = sk + SCAN_TC * dp;
+        if (ASYNC) {
+            if (kc + 1 < n_chunks) {
+                issue(kc + 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            if (a.act == 1) {
+                for (int idx = threadIdx.x; idx < n_tok * (2 * dp + VT); idx += 128) {
+                    // q and k rows lie back to back, the values behind them
+                    const int at = idx < n_tok * dp ? idx
+                                 : idx < 2 * n_tok * dp ? SCAN_TC * dp + (idx - n_tok * dp)
+                                                        : 2 * SCAN_TC * dp + (idx - 2 * n_tok * dp);
+                    const float x = sq[at];
+                    sq[at] = x / (1.0f + expf(-x));
+                }
+                __syncthreads();
+            }
+        } else {
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < n_tok * dp; idx += 128) {
+                const int tt = idx / dp, c = idx - tt * dp;
+                const X* row = base + (size_t)(q0 + t0 + tt) * a.ld;
+                sq[idx] = c < a.d ? read_act(row + a.q_off + h * a.d + c, a.act) : 0.0f;
+                sk[idx] = c < a.d ? read_act(row + a.k_off + h * a.d + c, a.act) : 0.0f;
+            }
+            for (int idx = threadIdx.x; idx < n_tok * VT; idx += 128) {
+                const int tt = idx / VT, c = idx - tt * VT;
+                const X* row = base + (size_t)(q0 + t0 + tt) * a.ld;
+                sv[idx] = v0 + c < a.dv ? read_act(row + a.v_off + h * a.dv + v0 + c, a.act) : 0.0f;
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        for (int tt = 0; tt < n_tok; ++tt) {
-            const float vv = sv[tt * VT + vcol];
-            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * dp);
-            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * dp);
-            float acc = 0.0f;
+        // A lane's part of every token's sum over d stays in a register of its own; only the two multiply-adds of a
+        // state wait for the token before.
+        float pv[SCAN_TC];
+        const float4* q4 = reinterpret_cast<const float4*>(sq) + ds;
+        const float4* k4 = reinterpret_cast<const float4*>(sk) + ds;
+        auto tokens = [&](auto full) {
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const int f = j * DS + ds;
-                if (f < dp4) {
-                    const float4 qq = q4[f], kk = k4[f];
-                    S[4 * j] = fmaf(kk.x, vv, fmaf(dm1, S[4 * j], S[4 * j]));
-                    S[4 * j + 1] = fmaf(kk.y, vv, fmaf(dm1, S[4 * j + 1], S[4 * j + 1]));
-                    S[4 * j + 2] = fmaf(kk.z, vv, fmaf(dm1, S[4 * j + 2], S[4 * j + 2]));
-                    S[4 * j + 3] = fmaf(kk.w, vv, fmaf(dm1, S[4 * j + 3], S[4 * j + 3]));
-                    acc = fmaf(S[4 * j], qq.x, acc);
-                    acc = fmaf(S[4 * j + 1], qq.y, acc);
-                    acc = fmaf(S[4 * j + 2], qq.z, acc);
-                    acc = fmaf(S[4 * j + 3], qq.w, acc);
+            for (int tt = 0; tt < SCAN_TC; ++tt) {
+                pv[tt] = 0.0f;
+                if (decltype(full)::value || tt < n_tok) {
+                    const float vv = sv[tt * VT + vcol];
+                    float ax = 0.0f, ay = 0.0f, az = 0.0f, aw = 0.0f;  // four sums side by side, joined in a fixed order
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) {
+                        if (EXACT || j * DS + ds < dp4) {
+                            const float4 qq = q4[tt * dp4 + j * DS], kk = k4[tt * dp4 + j * DS];
+                            S[4 * j] = fmaf(kk.x, vv, fmaf(dm1, S[4 * j], S[4 * j]));
+                            S[4 * j + 1] = fmaf(kk.y, vv, fmaf(dm1, S[4 * j + 1], S[4 * j + 1]));
+                            S[4 * j + 2] = fmaf(kk.z, vv, fmaf(dm1, S[4 * j + 2], S[4 * j + 2]));
+                            S[4 * j + 3] = fmaf(kk.w, vv, fmaf(dm1, S[4 * j + 3], S[4 * j + 3]));
+                            ax = fmaf(S[4 * j], qq.x, ax);
+                            ay = fmaf(S[4 * j + 1], qq.y, ay);
+                            az = fmaf(S[4 * j + 2], qq.z, az);
+                            aw = fmaf(S[4 * j + 3], qq.w, aw);
+                        }
+                    }
+                    pv[tt] = (ax + ay) + (az + aw);
                 }
             }
+        };
+        if (n_tok == SCAN_TC) tokens(std::true_type{});
+        else tokens(std::false_type{});
+        if (n_tok == 1) {                              // a single token: its sum alone crosses the lanes
+            float acc = pv[0];
             for (int o = DS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (ds == 0 && live) a.out[(size_t)(q0 + t0 + tt) * a.ldo + (size_t)h * a.dv + v] = acc;
+            if (ds == 0 && live) a.out[(size_t)(q0 + t0) * a.ldo + (size_t)h * a.dv + v] = acc;
+            if (ASYNC) __syncthreads();
+            continue;
         }
+        // The sixteen sums over a column's DS lanes, all at once: at every step a lane hands half of what it holds to
+        // the lane `o` away and adds what it gets to the half it keeps, so the lanes end with 16 / DS tokens each
+        // (fifteen shuffles instead of four a token).  `first` is the first token a lane ends up with.
+        int first = 0, held = SCAN_TC, o = DS >> 1;
+#define BROLM_FOLD(H)                                                              \
+        if (o > 0) {                                                               \
+            const bool up = (ds & o) != 0;                                         \
+            _Pragma("unroll") for (int i = 0; i < H; ++i) {                        \
+                const float send = up ? pv[i] : pv[i + H];                         \
+                const float keep = up ? pv[i + H] : pv[i];                         \
+                pv[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);              \
+            }                                                                      \
+            if (up) first += H;                                                    \
+            held = H;                                                              \
+            o >>= 1;                                                               \
+        }
+        BROLM_FOLD(8)
+        BROLM_FOLD(4)
+        BROLM_FOLD(2)
+        BROLM_FOLD(1)
+#undef BROLM_FOLD
+        bool writer = live;
+        if (o > 0) {                                   // 32 lanes a column: two lanes hold halves of one token's sum
+            pv[0] += __shfl_xor_sync(0xffffffffu, pv[0], o);
+            writer = writer && (ds & 1) == 0;
+        }
+#pragma unroll
+        float* orow = a.out + (size_t)(q0 + t0 + first) * a.ldo + (size_t)h * a.dv + v;
+#pragma unroll
+        for (int i = 0; i < SCAN_TC; ++i)
+            if (writer && i < held && first + i < n_tok) orow[(size_t)i * a.ldo] = pv[i];
+        if (ASYNC) __syncthreads();                    // the buffer is free for the chunk after the next
     }
     if (live) {
 #pragma unroll
@@ -121,36 +253,54 @@ __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
     }
 }
 
+template <typename X, int NJ, int DSC>
+int launch_scan_as(const ScanArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+    static size_t allowed = 0;
+    if (smem > 48 * 1024 && smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<X, NJ, DSC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed = smem;
+    }
+    // a prompt's scan runs long on few warps: plain stream order, so that its blocks spread evenly over the SMs
+    if (!a.early) return launch_in_order(decay_scan_kernel<X, NJ, DSC>, grid, dim3(128), smem, stream, a);
+    return launch_pdl(decay_scan_kernel<X, NJ, DSC>, grid, dim3(128), smem, stream, a);
+}
+
 template <typename X>
-int launch_scan(const ScanArgs& a0, int batch, cudaStream_t stream) {
+int launch_scan(const ScanArgs& a0, int batch, int max_q_len, cudaStream_t stream) {
     ScanArgs a = a0;
     const int dp4 = a.dp >> 2;
-    int nj = 1;
-    while (nj < 8 && nj * 4 < dp4) nj <<= 1;          // at most four lanes a column until a lane holds 32 states
-    int ds = 1;
-    while (ds * nj < dp4) ds <<= 1;
+    const int sms = device_sm_count();
+    // a lane keeps nj float4 of a column's states, ds lanes a column; fewer states a lane (more, smaller blocks)
+    // while the grid would leave SMs without a block
+    auto lanes = [&](int nj) { int ds = 1; while (ds * nj < dp4) ds <<= 1; return ds; };
+    auto blocks = [&](int nj) { const int vt = 128 / lanes(nj); return (long long)((a.dv + vt - 1) / vt) * a.heads * batch; };
+    int nj = 4;                                        // (eight would not leave the registers for sixteen tokens' sums)
+    while (nj > 1 && lanes(nj) == 1 && nj / 2 >= dp4) nj >>= 1;                      // no more registers than states
+    while (nj > 1 && lanes(nj / 2) <= 32 && blocks(nj) < sms) nj >>= 1;
+    const int ds = lanes(nj);
     if (ds > 32) return BROLM_ERR_TOO_LARGE;
     a.ds = ds;
+    a.early = max_q_len <= 1 ? 1 : 0;
     const int vt = 128 / ds;
-    const size_t smem = (size_t)SCAN_TC * (2 * a.dp + vt) * sizeof(float);
+    const bool async = sizeof(X) == 4;
+    const size_t smem = (size_t)(async ? 2 : 1) * SCAN_TC * (2 * a.dp + vt) * sizeof(float);
     if (smem > 200 * 1024) return BROLM_ERR_TOO_LARGE;
     dim3 grid((a.dv + vt - 1) / vt, a.heads, batch);
-#define BROLM_SCAN(NJ)                                                                                              \
-    do {                                                                                                            \
-        static size_t allowed = 0;                                                                                  \
-        if (smem > 48 * 1024 && smem > allowed) {                                                                   \
-            cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<X, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                                 (int)smem);                                                        \
-            if (e != cudaSuccess) return (int)e;                                                                    \
-            allowed = smem;                                                                                         \
-        }                                                                                                           \
-        return launch_pdl(decay_scan_kernel<X, NJ>, grid, dim3(128), smem, stream, a);                              \
-    } while (0)
-    if (nj == 1) BROLM_SCAN(1);
-    if (nj == 2) BROLM_SCAN(2);
-    if (nj == 4) BROLM_SCAN(4);
-    BROLM_SCAN(8);
-#undef BROLM_SCAN
+    if constexpr (sizeof(X) == 4) {
+        // the sizes of real layers (d = 32 .. 256 in whole lanes): everything about the row known to the compiler
+        if (a.vec && nj * ds == dp4 && a.d == a.dp) {
+            if (nj == 1 && ds == 8) return launch_scan_as<X, 1, 8>(a, grid, smem, stream);
+            if (nj == 2 && ds == 8) return launch_scan_as<X, 2, 8>(a, grid, smem, stream);
+            if (nj == 4 && ds == 8) return launch_scan_as<X, 4, 8>(a, grid, smem, stream);
+            if (nj == 1 && ds == 16) return launch_scan_as<X, 1, 16>(a, grid, smem, stream);
+            if (nj == 2 && ds == 16) return launch_scan_as<X, 2, 16>(a, grid, smem, stream);
+            if (nj == 4 && ds == 16) return launch_scan_as<X, 4, 16>(a, grid, smem, stream);
+        }
+    }
+    if (nj == 1) return launch_scan_as<X, 1, 0>(a, grid, smem, stream);
+    if (nj == 2) return launch_scan_as<X, 2, 0>(a, grid, smem, stream);
+    return launch_scan_as<X, 4, 0>(a, grid, smem, stream);
 }
 
 }  // namespace
@@ -159,7 +309,7 @@ int launch_scan(const ScanArgs& a0, int batch, cudaStream_t stream) {
 BROLM_API int brolm_decay_scan(const void* qkv, int x_dtype, long ld, int q_off, int k_off, int v_off, int heads, int d,
                                int dv, int act, const void* decay_m1, const void* cu_q, const void* kv_len,
                                const void* slots, void* state, long state_stride, void* out, long ldo, int batch,
-                               cudaStream_t stream) {
+                               int max_q_len, cudaStream_t stream) {
     if (batch <= 0) return BROLM_OK;
     if (heads <= 0 || d <= 0 || dv <= 0 || act < 0 || act > 1) return BROLM_ERR_BAD_SIZE;
     if (heads > 65535 || batch > 65535) return BROLM_ERR_TOO_LARGE;
@@ -169,8 +319,10 @@ BROLM_API int brolm_decay_scan(const void* qkv, int x_dtype, long ld, int q_off,
     a.heads = heads; a.d = d; a.dv = dv; a.dp = (d + 3) & ~3; a.act = act;
     a.decay_m1 = (const float*)decay_m1;
     a.cu_q = (const int32_t*)cu_q; a.kv_len = (const int32_t*)kv_len; a.slots = (const int32_t*)slots;
-    a.state = (float*)state; a.state_stride = state_stride; a.out = (float*)out; a.ldo = ldo; a.ds = 1;
-    if (x_dtype == BROLM_F32) return launch_scan<float>(a, batch, stream);
-    if (x_dtype == BROLM_BF16) return launch_scan<bf16>(a, batch, stream);
+    a.state = (float*)state; a.state_stride = state_stride; a.out = (float*)out; a.ldo = ldo; a.ds = 1; a.early = 0;
+    a.vec = x_dtype == BROLM_F32 && d % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 &&
+            v_off % 4 == 0 && ((uintptr_t)qkv & 15) == 0;
+    if (x_dtype == BROLM_F32) return launch_scan<float>(a, batch, max_q_len, stream);
+    if (x_dtype == BROLM_BF16) return launch_scan<bf16>(a, batch, max_q_len, stream);
     return BROLM_ERR_BAD_DTYPE;
 }

@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
                                                               const X* __restrict__ x, long ldx,
                                                               const float* __restrict__ shared, int shared_parts,
                                                               long long shared_stride, float* __restrict__ out, int tokens,
-                                                              int hidden, const X* __restrict__ shared_gate) {
+                                                              int hidden, const X* __restrict__ shared_gate, int gate_vec) {
     __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
@@ -182,8 +182,18 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
         // one number per token: the logistic function of the gate row's product with the token's input, summed
         // in float by a fixed tree (every block of the token computes the same)
         float dot = 0.0f;
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-            dot = fmaf(to_float(shared_gate[i]), to_float(x[(size_t)t * ldx + i]), dot);
+        const X* xr = x + (size_t)t * ldx;
+        if (gate_vec) {                                  // eight numbers a load
+            for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+                float gv[8], xv[8];
+                load8(shared_gate + i, gv);
+                load8(xr + i, xv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dot = fmaf(gv[e], xv[e], dot);
+            }
+        } else {
+            for (int i = threadIdx.x; i < hidden; i += blockDim.x) dot = fmaf(to_float(shared_gate[i]), to_float(xr[i]), dot);
+        }
         dot = block_sum(dot, scratch);
         sg = 1.0f / (1.0f + expf(-dot));
     }
@@ -314,15 +324,17 @@ BROLM_API int brolm_experts_combine(const void* y, const void* ids, const void* 
                                     void* out, int tokens, int hidden, const void* shared_gate, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (!shared) shared_parts = 0;
+    const int gate_vec = shared_gate && hidden % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 31) == 0 &&
+                         ((uintptr_t)shared_gate & 31) == 0;
     dim3 grid(tokens, (hidden + 255) / 256);
     if (x_dtype == BROLM_F32)
         return launch_pdl(experts_combine_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
                           (const float*)wts, top, n_real, (const float*)x, ldx, (const float*)shared, shared_parts,
-                          shared_stride, (float*)out, tokens, hidden, (const float*)shared_gate);
+                          shared_stride, (float*)out, tokens, hidden, (const float*)shared_gate, gate_vec);
     if (x_dtype == BROLM_BF16)
         return launch_pdl(experts_combine_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
                           (const float*)wts, top, n_real, (const bf16*)x, ldx, (const float*)shared, shared_parts,
-                          shared_stride, (float*)out, tokens, hidden, (const bf16*)shared_gate);
+                          shared_stride, (float*)out, tokens, hidden, (const bf16*)shared_gate, gate_vec);
     return BROLM_ERR_BAD_DTYPE;
 }
 

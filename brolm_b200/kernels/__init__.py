@@ -832,12 +832,13 @@ def decay_state_size(heads: int, dim: int, v_dim: int) -> int:
 
 def decay_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int, v_dim: int, activation: str,
                decay_m1: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
-               out: torch.Tensor, batch: int) -> None:
+               out: torch.Tensor, batch: int, max_q_len: int = 0) -> None:
     """Linear attention with a fixed decay per head over the packed tokens: S <- decay_h S + k v^T, out = S^T q.
     q, k (``dim`` per head) and v (``v_dim`` per head) are columns of ``qkv`` (tokens, cols) from ``q_off``, ``k_off``,
     ``v_off`` on, head by head; ``activation`` ("none", "silu") is applied to them as they are read.  ``decay_m1``
     float32 [heads] holds decay - 1.  S is the first ``decay_state_size`` floats of ``state[slot]``.  ``out`` float32
-    (tokens, heads * v_dim)."""
+    (tokens, heads * v_dim).  ``max_q_len`` 1 says that every sequence brings one token (the launch then takes part
+    in programmatic launch); 0: unknown."""
     assert qkv.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (qkv.shape[0], heads * v_dim)
     assert decay_m1.dtype == torch.float32 and decay_m1.is_contiguous() and decay_m1.numel() == heads
     assert max(q_off, k_off) + heads * dim <= qkv.shape[1] and v_off + heads * v_dim <= qkv.shape[1]
@@ -846,9 +847,10 @@ def decay_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int
         raise KernelError(f"decay_scan: unknown activation '{activation}'")
     f = _fn("linear_attn", "brolm_decay_scan", [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long,
-                                                c_int, c_void_p])
+                                                c_int, c_int, c_void_p])
     _check(f(_ptr(qkv), _code(qkv), qkv.stride(0), q_off, k_off, v_off, heads, dim, v_dim, SCAN_ACTS[activation],
-             _ptr(decay_m1), *_seq(cu_q, kv_len, slots, state), _ptr(out), out.stride(0), batch, _stream()), "decay_scan")
+             _ptr(decay_m1), *_seq(cu_q, kv_len, slots, state), _ptr(out), out.stride(0), batch, int(max_q_len), _stream()),
+           "decay_scan")
 
 
 def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:

@@ -240,8 +240,15 @@ class DecayLinearAttention(Part):
         T = x.shape[0]
         proj = linear(x, self.w_in, out_dtype=torch.float32)              # [ q | k | v | gate logits ]
         y = torch.empty((T, self.v_cols), dtype=torch.float32, device=x.device)
-        kernels.decay_scan(proj, 0, self.qk_cols, 2 * self.qk_cols, self.heads, self.dim, self.v_dim, self.activation,
-                           self.decay_m1, ctx.cu_q, ctx.kv_len, ctx.slots_dev, ctx.state(entry), y, ctx.batch)
+        act = self.activation
+        if act != "none" and ctx.max_q_len > 1:
+            # a prompt: every block of a head's scan would apply the activation to the head's q and k anew, so it
+            # is applied once, in place, by a pass of its own; a step of single tokens leaves it to the scan
+            qkv = proj[:, :2 * self.qk_cols + self.v_cols]
+            kernels.bias_act(qkv, None, act, qkv)
+            act = "none"
+        kernels.decay_scan(proj, 0, self.qk_cols, 2 * self.qk_cols, self.heads, self.dim, self.v_dim, act,
+                           self.decay_m1, ctx.cu_q, ctx.kv_len, ctx.slots_dev, ctx.state(entry), y, ctx.batch, ctx.max_q_len)
         if self.has_norm or self.has_gate:
             out = torch.empty((T, self.v_cols), dtype=ctx.dtype, device=x.device)
             if self.has_gate:
