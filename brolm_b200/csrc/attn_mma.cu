@@ -6,7 +6,8 @@
 BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int out_stride, const void* cu_q,
                                      const void* k, const void* v, int kv_stride, int n_kv, int group, int hd,
                                      float scale, float cap, int window, const void* sink, int batch,
-                                     int max_q_len, int chunk, cudaStream_t stream) {
+                                     int max_q_len, int chunk, const void* dist_bias, int dist_len,
+                                     cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     int st = check_common(hd, group, n_kv, q_stride, out_stride, batch);
     if (st) return st;
@@ -16,6 +17,8 @@ BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int
     a.cu_q = (const int32_t*)cu_q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.kv_stride = kv_stride;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.n_splits = 1; a.chunk = chunk;
     a.sink = (const float*)sink;
+    if (dist_bias && dist_len <= 0) return BROLM_ERR_BAD_SIZE;
+    a.dist_bias = (const float*)dist_bias; a.dist_len = dist_bias ? dist_len : 0;
     a.sms = device_sm_count();
     if (hd == 64) return launch_prefill<64, true>(a, batch, max_q_len, stream);
     if (hd == 128) return launch_prefill<128, true>(a, batch, max_q_len, stream);
@@ -33,7 +36,7 @@ BROLM_API int brolm_attn_decode_mma(const void* q, int q_stride, void* out, int 
                                     const void* page_table, int pt_stride, int ring, int page_size, int n_kv,
                                     int group, int hd, float scale, float cap, int window, const void* sink,
                                     int batch, int n_splits, void* part_o, void* part_ml, int chunk,
-                                    cudaStream_t stream) {
+                                    const void* dist_bias, int dist_len, cudaStream_t stream) {
     if (batch <= 0) return BROLM_OK;
     int st = check_common(hd, group, n_kv, q_stride, out_stride, batch);
     if (st) return st;
@@ -49,6 +52,8 @@ BROLM_API int brolm_attn_decode_mma(const void* q, int q_stride, void* out, int 
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.chunk = chunk;
     a.n_splits = n_splits; a.part_o = (float*)part_o; a.part_ml = (float*)part_ml;
     a.sink = (const float*)sink; a.shared_kv = k_pages == v_pages;
+    if (dist_bias && dist_len <= 0) return BROLM_ERR_BAD_SIZE;
+    a.dist_bias = (const float*)dist_bias; a.dist_len = dist_bias ? dist_len : 0;
     if (hd == 64) return launch_decode<64, true>(a, batch, stream);
     if (hd == 128) return launch_decode<128, true>(a, batch, stream);
     if (hd == 256) return launch_decode<256, true>(a, batch, stream);

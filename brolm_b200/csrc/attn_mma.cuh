@@ -110,6 +110,10 @@ struct MmaArgs {
     int merge_here;         // decoding: the last block of a (sequence, kv head) merges the splits itself
     const float* sink;      // [n_q] or null: exp(sink[head]) joins the softmax's denominator, with no value
     int shared_kv;          // decoding: the values are the keys' rows themselves (one tile serves both)
+    // a learned bias by distance, or null: [n_q][dist_len] floats, of which key j adds entry
+    // min(p - j, dist_len - 1) of its head's row to the score after the scale and the cap
+    const float* dist_bias;
+    int dist_len;
 };
 
 // Tickets of the split-KV decode kernel, one per (sequence, kv head); zero between launches.
@@ -192,10 +196,15 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
 
     // positions of this thread's two rows (r and r + 8 of the warp's 16)
     int rpos[2];
+    const float* db[2];        // their heads' rows of the distance table, and its last entry in log2 units
+    float db_far[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = warp * 16 + (lane >> 2) + 8 * i;
         rpos[i] = r < rows_here ? (row0 + r) / a.group : -1;
+        const int head = g * a.group + (r < rows_here ? (row0 + r) % a.group : 0);
+        db[i] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
+        db_far[i] = a.dist_bias ? db[i][a.dist_len - 1] * LOG2E : 0.0f;
     }
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
@@ -238,11 +247,20 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
         // scale, soft-cap, mask
         const int tile_lo = t * KT, tile_hi = tile_lo + KT - 1;
         const bool edge = tile_hi > tok_lo || tile_lo < tok_hi - window + 1 || tile_lo < chunk_hi;
+        const bool far_tile = tok_lo - tile_hi >= a.dist_len - 1;      // every key of the tile reads the table's last entry
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = score_of(s[nt][e], a.scale, a.cap, inv_cap);
+                if (a.dist_bias) {
+                    if (far_tile) {
+                        v += db_far[e >> 1];
+                    } else {
+                        const int dist = rpos[e >> 1] - (tile_lo + nt * 8 + (lane & 3) * 2 + (e & 1));
+                        v = fmaf(db[e >> 1][min(max(dist, 0), a.dist_len - 1)], LOG2E, v);
+                    }
+                }
                 if (edge) {
                     const int kp = tile_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int p = rpos[e >> 1];
@@ -413,6 +431,14 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     for (int i = 0; i < HD_MAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
+    const float* db[2];        // the rows of the distance table of this thread's two heads
+    float db_far[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        db[r] = a.dist_bias ? a.dist_bias + (size_t)(g * a.group + (row < a.group ? row : 0)) * a.dist_len : nullptr;
+        db_far[r] = a.dist_bias ? db[r][a.dist_len - 1] * LOG2E : 0.0f;
+    }
 
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES - 2>();
@@ -438,12 +464,17 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
             }
         }
         const int kbase = t * KT + warp * 16 + (lane & 3) * 2;
+        const bool far_tile = pos - (t * KT + KT - 1) >= a.dist_len - 1;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kp = kbase + nt * 8 + (e & 1);
-                const float v = score_of(s[nt][e], a.scale, a.cap, inv_cap);
+                float v = score_of(s[nt][e], a.scale, a.cap, inv_cap);
+                if (a.dist_bias) {
+                    if (far_tile) v += db_far[e >> 1];
+                    else v = fmaf(db[e >> 1][min(max(pos - kp, 0), a.dist_len - 1)], LOG2E, v);
+                }
                 s[nt][e] = (kp >= key_lo && kp <= pos) ? v : -INFINITY;
             }
         }

@@ -1357,18 +1357,21 @@ def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:
 
 def attention_prefill_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                           n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int, batch: int,
-                          max_q_len: int, sink: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+                          max_q_len: int, sink: Optional[torch.Tensor] = None, chunk: int = 0,
+                          dist_bias: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention of whole prompts that start at position 0 (bfloat16, head_dim <= 256).
-    ``chunk`` > 0: a query at position p sees no key before p - p % chunk."""
+    ``chunk`` > 0: a query at position p sees no key before p - p % chunk.  ``dist_bias`` as in ``attention_simt``."""
     _check_sink(sink, n_kv * group)
+    _check_dist_bias(dist_bias, n_kv * group)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert k.stride(0) == v.stride(0) and cu_q.dtype == torch.int32
     f = _fn("attn_mma", "brolm_attn_prefill_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                    c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int,
-                                                   c_int, c_int, c_void_p])
+                                                   c_int, c_int, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(k), _ptr(v), k.stride(0), n_kv, group,
-             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, int(chunk), _stream()), "attention_prefill_mma")
+             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, int(chunk), _ptr(dist_bias),
+             dist_bias.shape[1] if dist_bias is not None else 0, _stream()), "attention_prefill_mma")
 
 
 def attention_prefill_tc_ok(head_dim: int, group: int) -> bool:
@@ -1464,7 +1467,8 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
                          k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor, *, ring: int,
                          page_size: int, n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int,
                          batch: int, n_splits: int, scratch: Optional[tuple] = None,
-                         sink: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+                         sink: Optional[torch.Tensor] = None, chunk: int = 0,
+                         dist_bias: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention of one new token per sequence over the paged cache
     (bfloat16, head_dim <= 256, group <= 16, pages of 64 keys).  With more than
     one split the partial results go through float32 scratch: ``scratch`` =
@@ -1491,10 +1495,11 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
     f = _fn("attn_mma", "brolm_attn_decode_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                   c_float, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                                  c_int, c_void_p])
+                                                  c_int, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k_pages), _ptr(v_pages),
              _ptr(page_table), page_table.stride(0), ring, page_size, n_kv, group, head_dim, scale, cap, window,
-             _ptr(sink), batch, n_splits, _ptr(part_o), _ptr(part_ml), int(chunk), _stream()), "attention_decode_mma")
+             _ptr(sink), batch, n_splits, _ptr(part_o), _ptr(part_ml), int(chunk), _ptr(dist_bias),
+             dist_bias.shape[1] if dist_bias is not None else 0, _stream()), "attention_decode_mma")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -351,8 +351,21 @@ class Attention(Part):
                       window=self.window or 0, batch=ctx.batch, max_q_len=ctx.max_q_len)
         out = torch.empty((T, self.n_q * self.v_dim), dtype=ctx.dtype, device=dev)
         scored = bool(self.softcap or self.has_sink or self.dist_bias is not None)     # options of the score itself
-        special = self.talk or self.gate or self.slopes is not None or self.keep_first or self.chunk or scored
-        if not special and self.v_dim == self.head_dim and self.head_dim % 16 == 0 and self._tensor_cores(ctx):
+        special = self.talk or self.gate or self.slopes is not None or self.keep_first or self.chunk
+        same_size = self.v_dim == self.head_dim and self.head_dim % 16 == 0 and self._tensor_cores(ctx)
+        if not special and same_size and scored and (ctx.mode == "prefill" or page == 64):
+            # key and value rows of one size: the plain layers' mma.sync kernels, which know the cap, the sink and
+            # the distance table (and stage keys and values through more buffers than the head-wise ones)
+            more = dict(sink=self.sink, dist_bias=self.dist_bias)
+            if ctx.mode == "prefill":
+                kernels.attention_prefill_mma(q, out, ctx.cu_q, k, v, **common, **more)
+            else:
+                splits = kernels.decode_splits(ctx.batch, self.n_kv, ctx.max_kv_len, self.window or 0,
+                                               ragged=getattr(ctx, "ragged", False))
+                kernels.attention_decode_mma(q, out, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring,
+                                             page_size=page, n_splits=splits, **more,
+                                             **{n: a for n, a in common.items() if n != "max_q_len"})
+        elif not special and not scored and same_size:
             # nothing the tensor-core kernels do not know: the same attention as a plain layer's
             if ctx.mode == "prefill":
                 self.attend_packed(q, k, v, out, ctx, common)

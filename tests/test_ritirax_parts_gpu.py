@@ -82,14 +82,21 @@ def test_a_key_that_carries_the_weight_at_every_step_of_the_table(dtype, H, G, h
                                           n_kv=G, group=H // G, head_dim=hd, v_dim=vd, scale=1.0, window=0, batch=1,
                                           max_q_len=T, cap=cap, sink=sink.to(DEV), dist_bias=dist_table(rel, far).to(DEV))
         close(out.view(T, H, vd), ref, dtype, "packed, tensor cores")
+        if hd == vd:
+            # ... and on the kernel for key and value rows of one size
+            out.zero_()
+            kernels.attention_prefill_mma(q.reshape(T, -1).to(DEV), out, cu, k.reshape(T, -1).to(DEV), v.reshape(T, -1).to(DEV),
+                                          n_kv=G, group=H // G, head_dim=hd, scale=1.0, cap=cap, window=0, batch=1,
+                                          max_q_len=T, sink=sink.to(DEV), dist_bias=dist_table(rel, far).to(DEV))
+            close(out.view(T, H, vd), ref, dtype, "packed, tensor cores, rows of one size")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_far_keys_from_scattered_pages(dtype):
+@pytest.mark.parametrize("dtype,vd", [(torch.float32, 48), (torch.bfloat16, 48), (torch.bfloat16, 16)])
+def test_far_keys_from_scattered_pages(dtype, vd):
     """Decoding: one query per sequence over pages in a scattered order with NaN in the places never written; the key
     that carries the weight lies at a page's last place, at the next page's first, and far beyond the table's end."""
     g = torch.Generator().manual_seed(7)
-    H, G, hd, vd, rows, far, page = 4, 2, 16, 48, 8, 40.0, 64
+    H, G, hd, rows, far, page = 4, 2, 16, 8, 40.0, 64
     lengths = [1, 64, 65, 130, 400, 41]
     targets = [0, 63, 64, 63, 5, 1]                                   # position of the key each sequence's query looks for
     rel = 3.0 * torch.randn(rows, H, generator=g)
@@ -137,6 +144,16 @@ def test_far_keys_from_scattered_pages(dtype):
                                              sink=sink.to(DEV), dist_bias=dist_table(rel, far).to(DEV))
             for b, n in enumerate(lengths):
                 close(out[b].view(H, vd), refs[b], dtype, f"sequence of {n}, tensor cores, {splits} splits")
+            if hd == vd:
+                out.zero_()
+                kernels.attention_decode_mma(torch.stack(qs).reshape(B, -1).to(DEV), out,
+                                             torch.arange(B + 1, dtype=torch.int32, device=DEV),
+                                             torch.tensor(lengths, dtype=torch.int32, device=DEV), kp.to(DEV), vp.to(DEV),
+                                             pt.to(DEV), ring=1 << 30, page_size=page, n_kv=G, group=H // G, head_dim=hd,
+                                             scale=1.0, cap=15.0, window=0, batch=B, n_splits=splits, sink=sink.to(DEV),
+                                             dist_bias=dist_table(rel, far).to(DEV))
+                for b, n in enumerate(lengths):
+                    close(out[b].view(H, vd), refs[b], dtype, f"sequence of {n}, rows of one size, {splits} splits")
 
 
 def test_a_sink_that_swallows_a_head():
