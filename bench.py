@@ -556,11 +556,12 @@ def kedasun_main(args, pk) -> int:
 
 
 # --arch ritirax: a lightning layer with a dense feed-forward, a capped attention layer, a latent attention layer and a
-# second lightning layer, the last three with routed experts (the sizes of the Neburax run of the same letter)
+# second lightning layer, the last three with routed experts (the sizes of the Neburax run of the same letter; the
+# latent layer has sixteen heads, the most a decode tile of the tensor-core kernel has rows for)
 RITIRAX_SIZES = {
-    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, lat_dim=64, lat_rot=64, lat_vdim=64, kv_rank=192,
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, lat_heads=16, lat_dim=64, lat_rot=64, lat_vdim=64, kv_rank=192,
               experts=32, groups=8, keep=4, top=4, ff=1024, shared=1024, dense_ff=4096, vocab=32768),
-    "m": dict(width=3072, heads=24, kv_heads=4, dim=128, vdim=128, lat_dim=128, lat_rot=64, lat_vdim=128, kv_rank=192,
+    "m": dict(width=3072, heads=24, kv_heads=4, dim=128, vdim=128, lat_heads=16, lat_dim=128, lat_rot=64, lat_vdim=128, kv_rank=192,
               experts=64, groups=8, keep=4, top=6, ff=1024, shared=2048, dense_ff=6144, vocab=65536),
 }
 
@@ -580,7 +581,7 @@ def ritirax_main(args, pk) -> int:
     decay = [1.0 - 2.0 ** (-3.0 - 7.0 * h / max(H - 1, 1)) for h in range(H)]
     light = dict(heads=H, dim=d, vdim=dv, decay=decay)
     attn = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, softcap=30.0, bias_max=128, bias_rows=32)
-    lat = dict(heads=H, dim=z["lat_dim"], rot_dim=z["lat_rot"], vdim=z["lat_vdim"], kv_rank=z["kv_rank"],
+    lat = dict(heads=z["lat_heads"], dim=z["lat_dim"], rot_dim=z["lat_rot"], vdim=z["lat_vdim"], kv_rank=z["kv_rank"],
                scale=(z["lat_dim"] + z["lat_rot"]) ** -0.5,
                rot=dict(base=10000.0, dims=z["lat_rot"], scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0)))
     layers = [dict(type="lightning", mixer=light, mlp=dict(kind="dense", ff=z["dense_ff"])),
@@ -617,7 +618,8 @@ def ritirax_main(args, pk) -> int:
         ("ritirax prefill", r["prefill_kernels"], [
             ("grouped_tc_kernel", 3 * 2.0 * T * top * ff * W * 3, "flops"),
             ("attn_headmix_prefill", 2.0 * H * (d + dv) * keys, "flops"),
-            ("attn_prefill_mma", 2.0 * H * 2 * row * keys, "flops"),
+            (f"attn_prefill_mma_kernel<{d}", 2.0 * H * (d + dv) * keys, "flops"),
+            (f"attn_prefill_mma_kernel<{row}", 2.0 * z["lat_heads"] * 2 * row * keys, "flops"),
             ("decay_scan", 2 * T * (H * (2 * d + dv) + H * dv) * 4.0, "bytes"),
         ]),
         ("closest prefill", nb["prefill_kernels"], [
@@ -629,7 +631,8 @@ def ritirax_main(args, pk) -> int:
         ("ritirax decode", r["decode_kernels"], [
             ("fast_kernel<64, 64, 4, false>", 3 * active * ff * W * 2.0 * 3, "bytes"),
             ("attn_headmix_decode", batch * context * G * (d + dv) * 2.0, "bytes"),
-            ("attn_decode_mma", batch * context * row * 2.0, "bytes"),
+            (f"attn_decode_mma_kernel<{d}", batch * context * G * (d + dv) * 2.0, "bytes"),
+            (f"attn_decode_mma_kernel<{row}", batch * context * row * 2.0, "bytes"),
             ("decay_scan", 2 * batch * H * d * dv * 4.0 * 2, "bytes"),
         ]),
         ("closest decode", nb["decode_kernels"], [
