@@ -62,6 +62,40 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const Y* __restrict__ y, 
     out[(size_t)r * ldo + c] = from_float<O>(row_act(v, act));
 }
 
+// The same over float sums, four neighbours a thread (every row and part begins at a multiple of 16 bytes).
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    uint2 packed;
+    *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = packed;
+}
+
+template <typename B, typename O>
+__global__ void __launch_bounds__(256) bias_act4_kernel(const float* y, int n_parts, long long part_stride, long ldy,
+                                                        const B* __restrict__ bias, int act, O* out, long ldo, int cols) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= cols) return;
+    const float* yr = y + (size_t)r * ldy + c;
+    const float4 first = *reinterpret_cast<const float4*>(yr);
+    float v[4] = {first.x, first.y, first.z, first.w};
+    for (int s = 1; s < n_parts; ++s) {
+        const float4 u = *reinterpret_cast<const float4*>(yr + (size_t)s * part_stride);
+        v[0] += u.x; v[1] += u.y; v[2] += u.z; v[3] += u.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (bias) v[e] += to_float(bias[c + e]);
+        v[e] = row_act(v[e], act);
+    }
+    store4(out + (size_t)r * ldo + c, v);              // (y and out may be the same rows: a thread reads what it writes first)
+}
+
 __global__ void __launch_bounds__(256) scaled_sum_kernel(const float* __restrict__ a, int a_parts, long long a_stride, float sa,
                                                          const float* __restrict__ b, int b_parts, long long b_stride, float sb,
                                                          float* __restrict__ out, long long n) {
@@ -164,8 +198,9 @@ __global__ void __launch_bounds__(256) gate_group_norm_kernel(const float* __res
 }
 
 // y [top][tokens][hidden] float (rows of choices that named an identity expert are never read), x the experts'
-// input, shared [parts][tokens][hidden] float or null.
-template <typename X>
+// input, shared [parts][tokens][hidden] float or null.  V: neighbours of a row a thread takes (four when hidden is a
+// multiple of four and every row begins at a multiple of 16 bytes, else one).
+template <typename X, int V>
 __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ ids,
                                                               const float* __restrict__ wts, int top, int n_real,
                                                               const X* __restrict__ x, long ldx,
@@ -176,7 +211,7 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     float sg = 1.0f;
     if (shared_gate && shared_parts > 0) {
         // one number per token: the logistic function of the gate row's product with the token's input, summed
@@ -198,6 +233,29 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
         sg = 1.0f / (1.0f + expf(-dot));
     }
     if (c >= hidden) return;
+    if constexpr (V == 4) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sh[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int k = 0; k < top; ++k) {
+            const int e = ids[(size_t)t * top + k];
+            const float w = wts[(size_t)t * top + k];
+            float4 v;
+            if (e < n_real) {
+                v = *reinterpret_cast<const float4*>(y + ((size_t)k * tokens + t) * hidden + c);
+            } else {
+                const X* xr = x + (size_t)t * ldx + c;
+                v = make_float4(to_float(xr[0]), to_float(xr[1]), to_float(xr[2]), to_float(xr[3]));
+            }
+            acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+            acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+        }
+        for (int s = 0; s < shared_parts; ++s) {
+            const float4 u = *reinterpret_cast<const float4*>(shared + (size_t)s * shared_stride + (size_t)t * hidden + c);
+            sh[0] += u.x; sh[1] += u.y; sh[2] += u.z; sh[3] += u.w;
+        }
+        *reinterpret_cast<float4*>(out + (size_t)t * hidden + c) =
+            make_float4(fmaf(sg, sh[0], acc[0]), fmaf(sg, sh[1], acc[1]), fmaf(sg, sh[2], acc[2]), fmaf(sg, sh[3], acc[3]));
+        return;
+    }
     float acc = 0.0f;
     for (int k = 0; k < top; ++k) {
         const int e = ids[(size_t)t * top + k];
@@ -258,6 +316,17 @@ BROLM_API int brolm_bias_act(const void* y, int y_dtype, int n_parts, long long 
                              cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return BROLM_OK;
     if (act < 0 || act > 3 || n_parts < 1) return BROLM_ERR_BAD_SIZE;
+    if (y_dtype == BROLM_F32 && cols % 4 == 0 && ldy % 4 == 0 && part_stride % 4 == 0 && ldo % 4 == 0 &&
+        ((uintptr_t)y & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        dim3 grid4(rows, (cols / 4 + 255) / 256);
+#define BROLM_BA4(B, O) return launch_pdl(bias_act4_kernel<B, O>, grid4, dim3(256), 0, stream, (const float*)y, n_parts, \
+                                          part_stride, ldy, (const B*)bias, act, (O*)out, ldo, cols)
+        if (bias_dtype == BROLM_F32 && out_dtype == BROLM_F32) BROLM_BA4(float, float);
+        if (bias_dtype == BROLM_F32 && out_dtype == BROLM_BF16) BROLM_BA4(float, bf16);
+        if (bias_dtype == BROLM_BF16 && out_dtype == BROLM_F32) BROLM_BA4(bf16, float);
+        if (bias_dtype == BROLM_BF16 && out_dtype == BROLM_BF16) BROLM_BA4(bf16, bf16);
+#undef BROLM_BA4
+    }
     dim3 grid(rows, (cols + 255) / 256);
 #define BROLM_BA(Y, B, O) return launch_pdl(bias_act_kernel<Y, B, O>, grid, dim3(256), 0, stream, (const Y*)y, n_parts, \
                                             part_stride, ldy, (const B*)bias, act, (O*)out, ldo, cols)
@@ -326,15 +395,22 @@ BROLM_API int brolm_experts_combine(const void* y, const void* ids, const void* 
     if (!shared) shared_parts = 0;
     const int gate_vec = shared_gate && hidden % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 31) == 0 &&
                          ((uintptr_t)shared_gate & 31) == 0;
-    dim3 grid(tokens, (hidden + 255) / 256);
-    if (x_dtype == BROLM_F32)
-        return launch_pdl(experts_combine_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
-                          (const float*)wts, top, n_real, (const float*)x, ldx, (const float*)shared, shared_parts,
-                          shared_stride, (float*)out, tokens, hidden, (const float*)shared_gate, gate_vec);
-    if (x_dtype == BROLM_BF16)
-        return launch_pdl(experts_combine_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
-                          (const float*)wts, top, n_real, (const bf16*)x, ldx, (const float*)shared, shared_parts,
-                          shared_stride, (float*)out, tokens, hidden, (const bf16*)shared_gate, gate_vec);
+    const bool by_four = hidden % 4 == 0 && shared_stride % 4 == 0 && ((uintptr_t)y & 15) == 0 &&
+                         ((uintptr_t)shared & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    dim3 grid(tokens, by_four ? (hidden / 4 + 255) / 256 : (hidden + 255) / 256);
+#define BROLM_EC(X, V) return launch_pdl(experts_combine_kernel<X, V>, grid, dim3(256), 0, stream, (const float*)y,       \
+                                         (const int32_t*)ids, (const float*)wts, top, n_real, (const X*)x, ldx,           \
+                                         (const float*)shared, shared_parts, shared_stride, (float*)out, tokens, hidden, \
+                                         (const X*)shared_gate, gate_vec)
+    if (x_dtype == BROLM_F32) {
+        if (by_four) BROLM_EC(float, 4);
+        BROLM_EC(float, 1);
+    }
+    if (x_dtype == BROLM_BF16) {
+        if (by_four) BROLM_EC(bf16, 4);
+        BROLM_EC(bf16, 1);
+    }
+#undef BROLM_EC
     return BROLM_ERR_BAD_DTYPE;
 }
 
@@ -345,7 +421,8 @@ BROLM_API int brolm_norm_sigmoid_gate(const void* y, int y_dtype, long ldy, cons
     if (tokens <= 0) return BROLM_OK;
     if (cols <= 0) return BROLM_ERR_BAD_SIZE;
     if (!w) w_dtype = BROLM_F32;
-#define BROLM_NG(Y, Z, W, O) return launch_pdl(norm_sigmoid_gate_kernel<Y, Z, W, O>, dim3(tokens), dim3(256), 0, stream,                                                (const Y*)y, ldy, (const Z*)z, ldz, (const W*)w, eps, cols, (O*)out, ldo)
+#define BROLM_NG(Y, Z, W, O) return launch_pdl(norm_sigmoid_gate_kernel<Y, Z, W, O>, dim3(tokens), dim3(256), 0, stream, \
+                                               (const Y*)y, ldy, (const Z*)z, ldz, (const W*)w, eps, cols, (O*)out, ldo)
 #define BROLM_NG2(Y, Z, W)                                    \
     do {                                                      \
         if (out_dtype == BROLM_F32) BROLM_NG(Y, Z, W, float); \
