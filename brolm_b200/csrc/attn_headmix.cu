@@ -68,7 +68,8 @@ __device__ __forceinline__ float hm_score(float s, float scale, float cap, float
 // ===========================================================================
 // prompts that start at position 0
 // ===========================================================================
-template <int HD_MAX, int VD_MAX>
+// SCORED: the launch has a cap, a sink or a distance table (a kernel of its own, so that the others carry none of it).
+template <int HD_MAX, int VD_MAX, bool SCORED = false>
 __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hd = a.hd, vd = a.vd, hd16 = hd >> 4, vd16 = vd >> 4, cpr_k = hd >> 3, cpr_v = vd >> 3;
@@ -146,10 +147,11 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
         rpos[i] = r < rows_here ? (row0 + r) / a.group : -1;
         const int head = g * a.group + (r < rows_here ? (row0 + r) % a.group : 0);
         slope2[i] = (a.slopes && r < rows_here) ? a.slopes[head] * LOG2E : 0.0f;
-        db[i] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
-        db_far[i] = a.dist_bias ? db[i][a.dist_len - 1] * LOG2E : 0.0f;
+        db[i] = (SCORED && a.dist_bias) ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
+        db_far[i] = (SCORED && a.dist_bias) ? db[i][a.dist_len - 1] * LOG2E : 0.0f;
     }
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
+    const float scale2 = a.scale * LOG2E;
 
     const uint32_t x = lane & 7;
     const uint32_t xhi_k = swz_k ? (x & 6u) << 4 : 0u, xhi_v = swz_v ? (x & 6u) << 4 : 0u;
@@ -187,16 +189,21 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
         // scale, distance bias, mask
         const int tile_lo = t * KT, tile_hi = tile_lo + KT - 1;
         const bool edge = tile_hi > tok_lo || tile_lo < tok_hi - window + 1;
-        const bool far_tile = a.dist_bias && tok_lo - tile_hi >= a.dist_len - 1;     // no read of the table in this tile
+        const bool far_tile = SCORED && a.dist_bias && tok_lo - tile_hi >= a.dist_len - 1;   // no read of the table in this tile
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kp = tile_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
                 const int p = rpos[e >> 1];
-                float v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], far_tile ? nullptr : db[e >> 1],
-                                   a.dist_len, p - kp);
-                if (far_tile) v += db_far[e >> 1];
+                float v;
+                if constexpr (SCORED) {
+                    v = hm_score(s[nt][e], a.scale, a.cap, inv_cap, slope2[e >> 1], far_tile ? nullptr : db[e >> 1],
+                                 a.dist_len, p - kp);
+                    if (far_tile) v += db_far[e >> 1];
+                } else {
+                    v = s[nt][e] * scale2 - slope2[e >> 1] * (float)(p - kp);
+                }
                 if (edge && !(p >= 0 && kp <= p && (p - kp < window || kp < keep))) v = -INFINITY;
                 s[nt][e] = v;
             }
@@ -264,7 +271,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_headmix_prefill_kernel(HmArgs a
         const int rr = warp * 16 + (lane >> 2) + 8 * r;
         if (rr >= rows_here) continue;
         const int row = row0 + rr, tok = row / a.group, head = g * a.group + row % a.group;
-        if (a.sink && m[r] > -INFINITY) sum += fast_exp2(a.sink[head] * LOG2E - m[r]);
+        if constexpr (SCORED) {
+            if (a.sink && m[r] > -INFINITY) sum += fast_exp2(a.sink[head] * LOG2E - m[r]);
+        }
         const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
         const size_t at = (size_t)(q0 + tok) * a.out_stride + ((size_t)head * a.n_vh + c_out) * vd + (lane & 3) * 2;
 #pragma unroll
@@ -823,18 +832,21 @@ __global__ void __launch_bounds__(NTHREADS_ALL) attn_headmix_decode_all_kernel(H
     finish_decode(a, reinterpret_cast<float*>(stage0), vda, 1, 0, b, g, g, split, q_row, NTHREADS_ALL);
 }
 
-template <int HD_MAX, int VD_MAX>
+template <int HD_MAX, int VD_MAX, bool SCORED = false>
 int launch_hm_prefill(const HmArgs& a, int batch, int max_q_len, cudaStream_t stream) {
+    if constexpr (!SCORED) {
+        if (a.cap > 0.0f || a.sink || a.dist_bias) return launch_hm_prefill<HD_MAX, VD_MAX, true>(a, batch, max_q_len, stream);
+    }
     const size_t smem = ((size_t)(BM + KT) * a.hd + (size_t)KT * a.vd) * sizeof(bf16);
     static size_t allowed = 0;
     if (smem > allowed) {
-        cudaError_t e = cudaFuncSetAttribute(attn_headmix_prefill_kernel<HD_MAX, VD_MAX>,
+        cudaError_t e = cudaFuncSetAttribute(attn_headmix_prefill_kernel<HD_MAX, VD_MAX, SCORED>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         allowed = smem;
     }
     dim3 grid((max_q_len * a.group + BM - 1) / BM, a.n_kv * a.n_vh, batch);
-    attn_headmix_prefill_kernel<HD_MAX, VD_MAX><<<grid, NTHREADS, smem, stream>>>(a);
+    attn_headmix_prefill_kernel<HD_MAX, VD_MAX, SCORED><<<grid, NTHREADS, smem, stream>>>(a);
     return launch_status();
 }
 

@@ -132,7 +132,8 @@ __device__ __forceinline__ float score_of(float s, float scale, float cap, float
 // prompts
 // ===========================================================================
 // EXACT: head_dim == HD_MAX, known to the compiler (all index arithmetic folds).
-template <int HD_MAX, bool EXACT>
+// BIAS: the launch has a distance table (a kernel of its own, so that the others carry none of its code).
+template <int HD_MAX, bool EXACT, bool BIAS = false>
 __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hd = EXACT ? HD_MAX : a.hd, hd16 = hd >> 4, cpr = hd >> 3;
@@ -203,8 +204,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
         const int r = warp * 16 + (lane >> 2) + 8 * i;
         rpos[i] = r < rows_here ? (row0 + r) / a.group : -1;
         const int head = g * a.group + (r < rows_here ? (row0 + r) % a.group : 0);
-        db[i] = a.dist_bias ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
-        db_far[i] = a.dist_bias ? db[i][a.dist_len - 1] * LOG2E : 0.0f;
+        db[i] = BIAS ? a.dist_bias + (size_t)head * a.dist_len : nullptr;
+        db_far[i] = BIAS ? db[i][a.dist_len - 1] * LOG2E : 0.0f;
     }
     const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = score_of(s[nt][e], a.scale, a.cap, inv_cap);
-                if (a.dist_bias) {
+                if constexpr (BIAS) {
                     if (far_tile) {
                         v += db_far[e >> 1];
                     } else {
@@ -349,7 +350,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
 constexpr int STAGES = 3;
 constexpr int PT_ROW = 512;          // entries of a page-table row kept in shared memory (32768 keys)
 
-template <int HD_MAX, bool EXACT>
+template <int HD_MAX, bool EXACT, bool BIAS = false>
 __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hd = EXACT ? HD_MAX : a.hd, hd16 = hd >> 4, cpr = hd >> 3;
@@ -436,8 +437,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + 8 * r;
-        db[r] = a.dist_bias ? a.dist_bias + (size_t)(g * a.group + (row < a.group ? row : 0)) * a.dist_len : nullptr;
-        db_far[r] = a.dist_bias ? db[r][a.dist_len - 1] * LOG2E : 0.0f;
+        db[r] = BIAS ? a.dist_bias + (size_t)(g * a.group + (row < a.group ? row : 0)) * a.dist_len : nullptr;
+        db_far[r] = BIAS ? db[r][a.dist_len - 1] * LOG2E : 0.0f;
     }
 
     for (int i = 0; i < n_tiles; ++i) {
@@ -471,7 +472,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
             for (int e = 0; e < 4; ++e) {
                 const int kp = kbase + nt * 8 + (e & 1);
                 float v = score_of(s[nt][e], a.scale, a.cap, inv_cap);
-                if (a.dist_bias) {
+                if constexpr (BIAS) {
                     if (far_tile) v += db_far[e >> 1];
                     else v = fmaf(db[e >> 1][min(max(pos - kp, 0), a.dist_len - 1)], LOG2E, v);
                 }
@@ -724,28 +725,34 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
     }
 }
 
-template <int HD_MAX, bool EXACT>
+template <int HD_MAX, bool EXACT, bool BIAS = false>
 int launch_prefill(const MmaArgs& a, int batch, int max_q_len, cudaStream_t stream) {
+    if constexpr (!BIAS) {
+        if (a.dist_bias) return launch_prefill<HD_MAX, EXACT, true>(a, batch, max_q_len, stream);
+    }
     const size_t smem = (size_t)(BM + 2 * KT) * a.hd * sizeof(bf16);
     static size_t allowed = 0;               // raised once per size, not at every launch
     if (smem > allowed) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD_MAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD_MAX, EXACT, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         allowed = smem;
     }
     dim3 grid((max_q_len * a.group + BM - 1) / BM, a.n_kv, batch);
-    attn_prefill_mma_kernel<HD_MAX, EXACT><<<grid, NTHREADS, smem, stream>>>(a);
+    attn_prefill_mma_kernel<HD_MAX, EXACT, BIAS><<<grid, NTHREADS, smem, stream>>>(a);
     return launch_status();
 }
 
-template <int HD_MAX, bool EXACT>
+template <int HD_MAX, bool EXACT, bool BIAS = false>
 int launch_decode(const MmaArgs& a, int batch, cudaStream_t stream) {
+    if constexpr (!BIAS) {
+        if (a.dist_bias) return launch_decode<HD_MAX, EXACT, true>(a, batch, stream);
+    }
     size_t smem = (size_t)(16 + STAGES * 2 * KT) * a.hd * sizeof(bf16);
     const size_t merge = (size_t)(8 * 16 + 4 * a.group * a.hd) * sizeof(float) + 16 * a.hd * sizeof(bf16);
     if (merge > smem) smem = merge;
     static size_t allowed = 0;
     if (smem > allowed) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD_MAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD_MAX, EXACT, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         allowed = smem;
     }
@@ -753,7 +760,7 @@ int launch_decode(const MmaArgs& a, int batch, cudaStream_t stream) {
     MmaArgs b = a;
     b.merge_here = a.n_splits > 1 && a.n_splits <= MAX_MERGED_SPLITS && (long long)batch * a.n_kv <= MAX_TICKETS &&
                    (size_t)(a.group * a.n_splits + a.group) * sizeof(float) <= smem - 16 * a.hd * sizeof(bf16);
-    int st = launch_pdl(attn_decode_mma_kernel<HD_MAX, EXACT>, grid, dim3(NTHREADS), smem, stream, b);
+    int st = launch_pdl(attn_decode_mma_kernel<HD_MAX, EXACT, BIAS>, grid, dim3(NTHREADS), smem, stream, b);
     if (st != 0 || a.n_splits == 1 || b.merge_here) return st;
     dim3 cgrid(a.n_kv * a.group, batch);
     return launch_pdl(attn_combine_kernel, cgrid, dim3(128), (a.n_splits + 33) * sizeof(float), stream,
