@@ -577,7 +577,7 @@ def ritirax_main(args, pk) -> int:
     torch.cuda.set_device(0)
     W, H, G, d, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
     moe = dict(kind="moe", expert=dict(ff=z["ff"]), shared=dict(ff=z["shared"]),
-               router=dict(experts=z["experts"], top=z["top"], scale=2.5, groups=dict(count=z["groups"], keep=z["keep"])))
+               router=dict(experts=z["experts"], top=z["top"], scale=2.0, groups=dict(count=z["groups"], keep=z["keep"])))
     decay = [1.0 - 2.0 ** (-3.0 - 7.0 * h / max(H - 1, 1)) for h in range(H)]
     light = dict(heads=H, dim=d, vdim=dv, decay=decay)
     attn = dict(heads=H, kv_heads=G, dim=d, vdim=dv, scale=d ** -0.5, softcap=30.0, bias_max=128, bias_rows=32)

@@ -73,7 +73,7 @@ CFG_T = dict(
 CFG_U = dict(
     architecture="Ritirax", vocab=64, width=32, norm=dict(eps=1e-5), embedding=dict(scale=5.5),
     layers=[latent(4, 16, 16, 16, 32, 0.18, 1000.0, scaling=(8.0, 64, 16.0, 2.0), mlp=moe(16, 4, 4, scale=1.0, groups=(2, 2))),
-            attention(4, 1, 32, 32, 0.18, 30.0, 200, 32, mlp=dense(24)),
+            attention(4, 1, 32, 32, 0.18, 25.0, 200, 32, mlp=dense(24)),
             lightning(2, 32, 64, (0.999, 1.0), mlp=moe(16, 2, 2, scale=3.0, shared=24)),
             attention(2, 2, 16, 48, 0.25, 0.0, 9, 4)])
 

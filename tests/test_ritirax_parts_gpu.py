@@ -44,7 +44,7 @@ def dist_table(rel, far):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,hd,vd,rows,far,cap", [(4, 2, 16, 8, 8, 40.0, 20.0), (3, 3, 12, 20, 7, 25.0, 0.0),
-                                                    (4, 1, 32, 32, 32, 200.0, 30.0), (2, 2, 64, 80, 16, 120.0, 5.0)])
+                                                    (4, 1, 32, 32, 32, 200.0, 30.0), (2, 2, 64, 96, 12, 90.0, 5.0)])
 def test_a_key_that_carries_the_weight_at_every_step_of_the_table(dtype, H, G, hd, vd, rows, far, cap):
     """Packed (a prompt): the last queries each look for one key at a distance where the table's row changes; the
     table's rows differ by several units, so a row that is one off moves the weights."""
@@ -172,7 +172,7 @@ def test_a_sink_that_swallows_a_head():
     close(out[:, 1], ref[:, 1], torch.float32)
 
 
-@pytest.mark.parametrize("E,top,groups,keep,tokens", [(8, 4, 4, 3, 50), (6, 3, 3, 2, 9), (4, 2, 4, 3, 300), (8, 2, 2, 1, 70),
+@pytest.mark.parametrize("E,top,groups,keep,tokens", [(10, 4, 5, 3, 50), (6, 3, 3, 2, 9), (4, 2, 4, 3, 300), (8, 2, 2, 1, 70),
                                                       (12, 5, 1, 1, 33), (64, 6, 8, 4, 300), (4, 4, 2, 2, 5)])
 def test_choice_among_groups(E, top, groups, keep, tokens):
     g = torch.Generator().manual_seed(E * 7 + top)
@@ -185,14 +185,14 @@ def test_choice_among_groups(E, top, groups, keep, tokens):
     for use_product in (False, True):
         if use_product:
             z = (x.double() @ router.double().T).float().to(DEV)
-            kernels.route_pick(z, top, ids, wts, "softmax", None, groups=groups, keep=keep, renorm=False, scale=2.5)
+            kernels.route_pick(z, top, ids, wts, "softmax", None, groups=groups, keep=keep, renorm=False, scale=1.75)
         else:
             kernels.route_topk(x.to(DEV), router.to(DEV), top, ids, wts, "softmax", None, groups=groups, keep=keep,
-                               renorm=False, scale=2.5)
+                               renorm=False, scale=1.75)
         for t in range(tokens):
             want = plain.choose_experts(s[t], top, groups, keep)
             assert ids[t].tolist() == want, (t, ids[t].tolist(), want)
-            assert torch.allclose(wts[t].double().cpu(), 2.5 * s[t][want], rtol=1e-5)
+            assert torch.allclose(wts[t].double().cpu(), 1.75 * s[t][want], rtol=1e-5)
     # the plain softmax router is what it was: weights over their sum
     kernels.route_topk(x.to(DEV), router.to(DEV), top, ids, wts, "softmax", None)
     assert torch.allclose(wts.sum(dim=1).cpu(), torch.ones(tokens), atol=1e-5)

@@ -27,7 +27,7 @@ def draw_mlp(rng, discrete):
     experts = count * rng.choice([1, 2, 3])
     keep = rng.randint(1, count) if discrete else count
     top = rng.randint(1, min(keep * (experts // count), 4)) if discrete else experts
-    return moe(rng.choice([8, 12, 40, 72]), experts, top, scale=rng.choice([None, 0.5, 2.5]),
+    return moe(rng.choice([8, 12, 40, 72]), experts, top, scale=rng.choice([None, 0.5, 1.75]),
                groups=(count, keep) if (count > 1 or rng.random() < 0.5) else None, shared=rng.choice([None, 8, 56]))
 
 
@@ -54,7 +54,7 @@ def draw_layer(rng, discrete, tensor_sizes):
 
 def draw_config(seed, discrete=True, tensor_sizes=False):
     rng = random.Random(seed)
-    return dict(architecture="Ritirax", vocab=rng.choice([37, 64, 200, 577]), width=rng.choice([24, 40, 72, 136, 320]),
+    return dict(architecture="Ritirax", vocab=rng.choice([37, 64, 200, 577]), width=rng.choice([24, 40, 72, 136, 312]),
                 norm=dict(eps=rng.choice([1e-5, 1e-6])), embedding=dict(scale=rng.choice([0.5, 1.0, 4.0, 12.0])),
                 layers=[draw_layer(rng, discrete, tensor_sizes) for _ in range(rng.randint(1, 5))])
 
